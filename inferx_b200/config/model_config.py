@@ -85,7 +85,11 @@ class _Reader:
 
 
 def read_architecture_name(obj: Mapping[str, Any], where: str = "config.json") -> str:
-    """The single entry of ``architectures`` (src/model/config.cc:283-294)."""
+    """The single entry of ``architectures`` (src/model/config.cc:283-294), or the string
+    ``architecture`` of configuration files that name their design that way."""
+    if isinstance(obj, Mapping) and "architectures" not in obj and isinstance(
+            obj.get("architecture"), str):
+        return obj["architecture"]
     archs = obj.get("architectures") if isinstance(obj, Mapping) else None
     if not isinstance(archs, list) or len(archs) != 1 or not isinstance(archs[0], str):
         raise ConfigError(f"{where}: 'architectures' must be a list with exactly one name")

@@ -56,6 +56,10 @@ def _register_builtin():
     from ..models import qwen2_moe
     register_architecture(Qwen2MoeConfig.ARCHITECTURE, Qwen2MoeConfig.from_json,
                           qwen2_moe.build_spec, replace=True)
+    from ..models import zuzisun
+    from .zuzisun_config import ZuzisunConfig
+    register_architecture(ZuzisunConfig.ARCHITECTURE, ZuzisunConfig.from_json,
+                          zuzisun.build_spec, replace=True)
 
 
 _register_builtin()

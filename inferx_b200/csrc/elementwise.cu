@@ -16,21 +16,22 @@ IX_API int ix_dependent_launch_flag(int set_to) {
 }
 
 // ---------------------------------------------------------------------------
-// embedding: out[t, :] = table[ids[t], :] widened to fp32 (the residual stream)
+// embedding: out[t, :] = table[ids[t], :] * scale, widened to fp32 (the residual stream)
 // ---------------------------------------------------------------------------
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
-                             float* __restrict__ out, int H, int V) {
+                             float* __restrict__ out, int H, int V, float scale) {
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= V) id = 0;  // host validates; never read out of range
   const TW* row = table + (size_t)id * H;
   float* o = out + (size_t)t * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]) * scale;
 }
 
 __global__ void embed_bf16_vec_kernel(const uint4* __restrict__ table, const int* __restrict__ ids,
-                                      float4* __restrict__ out, int chunks, int V) {
+                                      float4* __restrict__ out, int chunks, int V,
+                                      float scale) {
   IX_PDL_WAIT();
   const int t = blockIdx.x;
   int id = ids[t];
@@ -40,23 +41,24 @@ __global__ void embed_bf16_vec_kernel(const uint4* __restrict__ table, const int
   for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
     float f[8];
     bf8_to_f32(row[c], f);
-    o[2 * c] = make_float4(f[0], f[1], f[2], f[3]);
-    o[2 * c + 1] = make_float4(f[4], f[5], f[6], f[7]);
+    o[2 * c] = make_float4(f[0] * scale, f[1] * scale, f[2] * scale, f[3] * scale);
+    o[2 * c + 1] = make_float4(f[4] * scale, f[5] * scale, f[6] * scale, f[7] * scale);
   }
 }
 
 IX_API int ix_embed(const void* table, int table_dtype, const int* ids, int T, int H, int V,
-                    float* out, cudaStream_t stream) {
+                    float* out, float scale, cudaStream_t stream) {
   if (T <= 0) return IX_OK;
   if (H <= 0 || V <= 0) return IX_ERR_SIZE;
   const int threads = H >= 1024 ? 256 : 128;
   if (table_dtype == IX_BF16 && H % 8 == 0 && (((uintptr_t)table | (uintptr_t)out) & 15) == 0) {
     ix_launch(embed_bf16_vec_kernel, dim3(T), dim3(threads), 0, stream, (const uint4*)table, ids,
-              (float4*)out, H / 8, V);
+              (float4*)out, H / 8, V, scale);
     return ix_launch_status();
   }
   IX_DISPATCH_DTYPE(table_dtype, TW,
-                    (embed_kernel<TW><<<T, threads, 0, stream>>>((const TW*)table, ids, out, H, V)));
+                    (embed_kernel<TW><<<T, threads, 0, stream>>>((const TW*)table, ids, out, H, V,
+                                                                 scale)));
   return ix_launch_status();
 }
 

@@ -132,7 +132,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
-    ap.add_argument("--max-live", type=int, default=8, help="requests alive at once")
+    ap.add_argument("--max-live", type=int, default=4, help="requests alive at once")
     ap.add_argument("--index", action="store_true",
                     help="also write <step>.rows.json: request id and position of each row")
     args = ap.parse_args(argv)

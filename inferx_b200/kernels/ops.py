@@ -147,8 +147,9 @@ def check_router_limits(hidden: int, num_experts: int, top_k: int, where: str = 
         raise KernelError(f"{where}: {top_k} experts per token of {num_experts}")
 
 
-def embed(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None):
-    """out[t] = table[ids[t]] widened to fp32 (the residual stream)."""
+def embed(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None,
+          scale: float = 1.0):
+    """out[t] = table[ids[t]] * scale, widened to fp32 (the residual stream)."""
     _chk("table", table)
     _chk("ids", ids, torch.int32)
     V, H = table.shape
@@ -157,7 +158,7 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = 
         out = torch.empty((T, H), dtype=torch.float32, device=table.device)
     _chk("out", out, torch.float32)
     _check(_lib().ix_embed(_ptr(table), _dtype_code(table), _ptr(ids), T, H, V, _ptr(out),
-                           _stream()), "embed")
+                           ctypes.c_float(scale), _stream()), "embed")
     _count()
     return out
 
@@ -980,3 +981,182 @@ def gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor):
     if M <= SMALL_M_DENSE_ROWS and _streams_weights(x, w_gate_up):
         return gemm_small_m(x, w_gate_up.unsqueeze(0), None, None, True, M, rows_per_pass=M)
     return silu_mul(linear(x, w_gate_up))
+
+
+# ---------------------------------------------------------------------------
+# Parts of decoders that normalise a sublayer's output, shift tokens, gate or clamp
+# ---------------------------------------------------------------------------
+def token_shift(resid: torch.Tensor, mix: torch.Tensor, state: torch.Tensor, step,
+                out_dtype: torch.dtype):
+    """out[t] = x[t] + (x[t-1] - x[t]) * mix in fp32, returned in ``out_dtype``.  The row
+    before a sequence's first token of this step comes from ``state[state_slot[s]]``
+    ([slots, width] fp32), which then receives the sequence's last row of this step."""
+    _chk("resid", resid, torch.float32)
+    _chk("mix", mix, torch.float32)
+    _chk("state", state, torch.float32)
+    T, W = resid.shape
+    if mix.numel() != W or state.shape[1] != W:
+        raise KernelError("token_shift: mix and state must have the residual's width")
+    out = torch.empty((T, W), dtype=out_dtype, device=resid.device)
+    _check(_lib().ix_token_shift(_ptr(resid), _ptr(mix), _ptr(state), _ptr(step.cu_q),
+                                 _ptr(step.seq_of_token), _ptr(step.state_slot), _ptr(out),
+                                 _dtype_code(out), T, W, _stream()), "token_shift")
+    _count()
+    return out
+
+
+def group_norm_add(resid: torch.Tensor, delta: torch.Tensor, gain: torch.Tensor, groups: int,
+                   eps: float, cast_dtype: Optional[torch.dtype] = None):
+    """resid += grouped_rms_norm(delta) * gain, in place and in fp32: each row of ``delta``
+    in ``groups`` equal consecutive parts, each part over its own root mean square.
+    With ``cast_dtype`` the new residual is also returned in that element type."""
+    _chk("resid", resid, torch.float32)
+    _chk("delta", delta)
+    _chk("gain", gain, torch.float32)
+    T, W = resid.shape
+    if delta.shape != resid.shape or gain.numel() != W:
+        raise KernelError("group_norm_add: delta and gain must match the residual")
+    if groups <= 0 or W % groups:
+        raise KernelError(f"group_norm_add: width {W} does not split into {groups} equal parts")
+    cast = (torch.empty((T, W), dtype=cast_dtype, device=resid.device)
+            if cast_dtype is not None else None)
+    _check(_lib().ix_group_norm_add(
+        _ptr(resid), _ptr(delta), _dtype_code(delta), _ptr(gain), _ptr(cast),
+        _dtype_code(cast) if cast is not None else _dtype_code(delta), T, W, groups,
+        ctypes.c_float(eps), _stream()), "group_norm_add")
+    _count()
+    return cast
+
+
+def group_norm_rows(resid: torch.Tensor, rows: Optional[torch.Tensor], gain: torch.Tensor,
+                    groups: int, eps: float, out_dtype: torch.dtype):
+    """grouped_rms_norm(resid[rows]) * gain in ``out_dtype`` (every row when ``rows`` is None)."""
+    _chk("resid", resid, torch.float32)
+    _chk("rows", rows, torch.int32, optional=True)
+    _chk("gain", gain, torch.float32)
+    T, W = resid.shape
+    if gain.numel() != W or groups <= 0 or W % groups:
+        raise KernelError(f"group_norm_rows: width {W}, gain {gain.numel()}, groups {groups}")
+    R = T if rows is None else rows.numel()
+    out = torch.empty((R, W), dtype=out_dtype, device=resid.device)
+    _check(_lib().ix_group_norm_rows(_ptr(resid), _ptr(rows), _ptr(gain), _ptr(out),
+                                     _dtype_code(out), R, W, groups, ctypes.c_float(eps),
+                                     _stream()), "group_norm_rows")
+    _count()
+    return out
+
+
+def glu_clamped(gu: torch.Tensor, limit: float, alpha: float, up_shift: float):
+    """[T, 2I] (gate | up) -> min(g, L) * sigmoid(alpha * min(g, L)) * (clamp(u, -L, L) + up_shift)."""
+    _chk("gu", gu)
+    T, two_i = gu.shape
+    if two_i % 2:
+        raise KernelError("glu_clamped: width must be even (gate | up)")
+    out = torch.empty((T, two_i // 2), dtype=gu.dtype, device=gu.device)
+    _check(_lib().ix_glu_clamped(_ptr(gu), _ptr(out), _dtype_code(gu), T, two_i // 2,
+                                 ctypes.c_float(limit), ctypes.c_float(alpha),
+                                 ctypes.c_float(up_shift), _stream()), "glu_clamped")
+    _count()
+    return out
+
+
+def gate_up_glu_clamped(x: torch.Tensor, w_gate_up: torch.Tensor, limit: float, alpha: float,
+                        up_shift: float):
+    """Front half of a clamped-GLU feed-forward: the fused gate|up product, then the
+    activation."""
+    return glu_clamped(linear(x, w_gate_up), limit, alpha, up_shift)
+
+
+def batched_linear(x: torch.Tensor, w: torch.Tensor):
+    """out[b] = x[b] . w[b]^T for x [B, M, K] (any strides with unit inner stride) and
+    w [B, N, K]: one library call batched over the leading dimension (per-head
+    products).  float32 operands are multiplied in true 32-bit."""
+    if not (x.is_cuda and w.is_cuda):
+        raise KernelError("batched_linear: tensors must be on a CUDA device")
+    if x.dtype != w.dtype or x.dim() != 3 or w.dim() != 3 or x.shape[0] != w.shape[0] \
+            or x.shape[2] != w.shape[2]:
+        raise KernelError(f"batched_linear: {tuple(x.shape)} {x.dtype} against "
+                          f"{tuple(w.shape)} {w.dtype}")
+    if x.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
+        raise KernelError("batched_linear: TF32 is switched on; 32-bit products must be exact")
+    LIBRARY_CALLS[0] += 1
+    return torch.bmm(x, w.transpose(1, 2))
+
+
+def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int, positions: torch.Tensor,
+                   freq: torch.Tensor, mag: float, gain: torch.Tensor, eps: float, heads: int,
+                   dim: int, rot_dim: int, rot_dims: int, rank: int,
+                   cache: Optional[torch.Tensor], slots: Optional[torch.Tensor]):
+    """From the fused projection ``proj`` [T, *]: RMS-norm the latent (columns ``kv_off`` ..
+    + rank), rotate the shared key part behind it and each head's rotated query part
+    (head h's query is ``dim`` plain then ``rot_dim`` rotated columns from ``q_off`` on;
+    interleaved pairs, the first ``rot_dims`` entries turn), write the record
+    [latent | rotated key] into ``cache`` ([pages, 1, page, rank + rot_dim]) at ``slots``.
+    Returns the rotated query parts [T, heads, rot_dim]."""
+    _chk("proj", proj)
+    _chk("positions", positions, torch.int32)
+    _chk("freq", freq, torch.float32)
+    _chk("gain", gain, torch.float32)
+    _chk("cache", cache, proj.dtype, optional=True)
+    _chk("slots", slots, torch.int32, optional=True)
+    T, ld = proj.shape
+    if q_off + heads * (dim + rot_dim) > ld or kv_off + rank + rot_dim > ld:
+        raise KernelError("latent_prepare: the projection is narrower than its parts")
+    if freq.numel() * 2 != rot_dims or gain.numel() != rank:
+        raise KernelError("latent_prepare: one frequency per rotated pair, one gain per latent")
+    if cache is not None and (cache.shape[1] != 1 or cache.shape[3] != rank + rot_dim):
+        raise KernelError("latent_prepare: cache records must be [1, page, rank + rot_dim]")
+    q_rot = torch.empty((T, heads, rot_dim), dtype=proj.dtype, device=proj.device)
+    _check(_lib().ix_latent_prepare(
+        _ptr(proj), ctypes.c_longlong(ld), q_off, kv_off, _ptr(positions), _ptr(freq),
+        ctypes.c_float(mag), _ptr(gain), ctypes.c_float(eps), _ptr(slots), _ptr(cache),
+        _ptr(q_rot), _dtype_code(proj), T, heads, dim, rot_dim, rot_dims, rank, _stream()),
+        "latent_prepare")
+    _count()
+    return q_rot
+
+
+def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, cache: torch.Tensor,
+                     block_table: torch.Tensor, step, window: int, scale: float):
+    """Attention of this step's queries over cached latent records.
+
+    ``q_lat`` [heads, T, rank] (the query with the key matrix folded in), ``q_rot``
+    [T, heads, rot_dim], ``cache`` [pages, 1, page, rank + rot_dim].  Scores are
+    (q_lat . latent + q_rot . key_rot) * scale over the keys a position sees (itself and
+    the ``window`` - 1 before it; all earlier ones when ``window`` is 0); returns
+    sum_j p_j latent_j as [heads, T, rank]."""
+    _chk("q_lat", q_lat)
+    _chk("q_rot", q_rot, q_lat.dtype)
+    _chk("cache", cache, q_lat.dtype)
+    _chk("block_table", block_table, torch.int32)
+    H, T, rank = q_lat.shape
+    dr = q_rot.shape[2]
+    P, one, page, dk = cache.shape
+    if one != 1 or dk != rank + dr or q_rot.shape[:2] != (T, H):
+        raise KernelError("latent_attention: queries and cache records disagree")
+    out = torch.empty((H, T, rank), dtype=q_lat.dtype, device=q_lat.device)
+    _check(_lib().ix_latent_attention(
+        _ptr(q_lat), ctypes.c_longlong(T * rank), ctypes.c_longlong(rank), _ptr(q_rot),
+        _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(step.seq_of_token),
+        _ptr(step.positions), _ptr(out), ctypes.c_longlong(T * rank), ctypes.c_longlong(rank),
+        _dtype_code(q_lat), T, H, rank, dr, page, window, ctypes.c_float(scale), _stream()),
+        "latent_attention")
+    _count()
+    return out
+
+
+def gate_heads(o: torch.Tensor, proj: torch.Tensor, gate_off: int):
+    """out[t, h * D + j] = o[h, t, j] * sigmoid(proj[t, gate_off + h * D + j]) for
+    o [heads, T, D]: the output gate, with the heads laid beside each other again."""
+    _chk("o", o)
+    _chk("proj", proj, o.dtype)
+    H, T, D = o.shape
+    if proj.shape[0] != T or gate_off + H * D > proj.shape[1]:
+        raise KernelError("gate_heads: the gate columns do not fit the projection")
+    out = torch.empty((T, H * D), dtype=o.dtype, device=o.device)
+    gate = proj.view(-1)[gate_off:]
+    _check(_lib().ix_gate_heads(_ptr(o), ctypes.c_void_p(gate.data_ptr()),
+                                ctypes.c_longlong(proj.shape[1]), _ptr(out), _dtype_code(o), T, H,
+                                D, _stream()), "gate_heads")
+    _count()
+    return out

@@ -51,6 +51,51 @@ class PreNormBlock:
         return self.ffn.forward(n, step)
 
 
+class SublayerNormBlock:
+    """``x += norm(mixer(shift(x))); x += norm(ffn(x))`` on the fp32 residual stream: the
+    sublayers read the stream itself and their OUTPUT is normalised before it is added.
+    ``spec.input_norm`` follows the mixer, ``spec.post_norm`` the feed-forward;
+    ``spec.mixer_input`` transforms what the mixer reads and may keep state per request.
+    A layer may have no feed-forward."""
+
+    def __init__(self, spec, ctx: BuildContext, prefix: str):
+        p = prefix
+        self.spec, self.ctx = spec, ctx
+        self.mixer_input = build_part("mixer_input", spec.mixer_input, ctx,
+                                      f"{p}.{spec.mixer_input_name}")
+        self.mixer = build_part("mixer", spec.mixer, ctx, f"{p}.{spec.mixer_name}")
+        self.mixer_norm = build_part("norm", spec.input_norm, ctx, f"{p}.{spec.input_norm_name}")
+        self.ffn = build_part("feed_forward", spec.ffn, ctx, f"{p}.{spec.ffn_name}")
+        self.ffn_norm = (build_part("norm", spec.post_norm, ctx, f"{p}.{spec.post_norm_name}")
+                         if self.ffn is not None else None)
+
+    def parts(self):
+        return [x for x in (self.mixer_input, self.mixer, self.mixer_norm, self.ffn,
+                            self.ffn_norm) if x is not None]
+
+    def cache_needs(self):
+        needs = list(self.mixer.cache_needs())
+        if self.mixer_input is not None:
+            needs += list(self.mixer_input.cache_needs())
+        return needs
+
+    def forward(self, resid, pending, step: StepContext, cache: LayerCache):
+        if pending is not None:     # a block of another arrangement ran before this one
+            if hasattr(pending, "materialize"):
+                pending = pending.materialize()
+            resid.add_(pending.to(resid.dtype))
+        dt = self.ctx.dtype
+        h = (self.mixer_input.forward(resid, step, cache) if self.mixer_input is not None
+             else resid.to(dt))
+        a = self.mixer.forward(h, step, cache)
+        if self.ffn is None:
+            self.mixer_norm.add_normed(resid, a)
+            return None
+        n = self.mixer_norm.add_normed(resid, a, cast_dtype=dt)
+        self.ffn_norm.add_normed(resid, self.ffn.forward(n, step))
+        return None
+
+
 class DecoderModel:
     """Embedding, scheduled blocks, final norm and head, from a ``ModelSpec``."""
 
@@ -116,7 +161,10 @@ class DecoderModel:
         ops = self.ctx.ops
         if hasattr(ops, "set_dependent_launch"):
             ops.set_dependent_launch(step.num_tokens <= ops.DEPENDENT_LAUNCH_MAX_TOKENS)
-        resid = ops.embed(self.embed, step.token_ids)
+        if self.spec.embed_scale != 1.0:
+            resid = ops.embed(self.embed, step.token_ids, scale=self.spec.embed_scale)
+        else:
+            resid = ops.embed(self.embed, step.token_ids)
         pending = None
         for entry, cache in zip(self.spec.schedule, caches):
             pending = self.blocks[entry.layer].forward(resid, pending, step, cache)
@@ -131,3 +179,4 @@ class DecoderModel:
 
 Block = PreNormBlock
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "sublayer_norm", SublayerNormBlock)

@@ -44,6 +44,37 @@ class SwiGluFeedForward:
         return ops.linear(ops.gate_up_swiglu(x, self.gate_up_w), self.down_w)
 
 
+class ClampedGluFeedForward:
+    """``down(min(g, L) * sigmoid(alpha * min(g, L)) * (clamp(u, -L, L) + up_shift))``: a
+    gated unit whose gate is cut off above and whose linear branch is cut off on both
+    sides before one is added to it.  Gate and up are one product over concatenated
+    weights; the result leaves in fp32 for the norm that follows."""
+
+    def __init__(self, spec, ctx, prefix: str):
+        self.spec, self.ctx, self.prefix = spec, ctx, prefix
+        self.gate_up_w = self.down_w = None
+
+    def tensors(self):
+        s, p = self.spec, self.prefix
+        g, u, d = s.names
+        return [
+            TensorDecl(f"{p}.{g}", (s.intermediate, s.hidden)),
+            TensorDecl(f"{p}.{u}", (s.intermediate, s.hidden)),
+            TensorDecl(f"{p}.{d}", (s.hidden, s.intermediate)),
+        ]
+
+    def bind(self, w):
+        p = self.prefix
+        g, u, d = self.spec.names
+        self.gate_up_w = torch.cat([w[f"{p}.{g}"], w[f"{p}.{u}"]], dim=0).contiguous()
+        self.down_w = w[f"{p}.{d}"]
+
+    def forward(self, x, step=None):
+        s, ops = self.spec, self.ctx.ops
+        act = ops.gate_up_glu_clamped(x, self.gate_up_w, s.limit, s.alpha, s.up_shift)
+        return ops.linear(act, self.down_w, out_dtype=torch.float32)
+
+
 _SIDE_STREAMS: dict = {}
 
 
@@ -196,3 +227,4 @@ class MoeFeedForward:
 
 register_part("feed_forward", "swiglu", SwiGluFeedForward)
 register_part("feed_forward", "moe", MoeFeedForward)
+register_part("feed_forward", "clamped_glu", ClampedGluFeedForward)

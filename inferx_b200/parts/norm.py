@@ -35,3 +35,41 @@ class RmsNorm:
 
 
 register_part("norm", "rmsnorm", RmsNorm)
+
+
+class GroupedRmsNorm:
+    """RMS norm in groups: a row is cut into ``groups`` equal consecutive parts, each is
+    divided by its own sqrt(mean(part^2) + eps), and the whole row is multiplied by the
+    gain; all in fp32.  Two uses: ``add_normed`` normalises a sublayer's output and adds
+    it into the residual stream (x += norm(f(x))); ``forward`` normalises rows of the
+    residual stream itself (the model's last norm)."""
+
+    def __init__(self, spec, ctx, prefix: str):
+        self.spec = spec
+        self.ctx = ctx
+        self.name = prefix
+        self.gain = None
+        if spec.groups <= 0 or spec.size % spec.groups:
+            raise ValueError(f"{prefix}: {spec.size} entries do not split into {spec.groups} "
+                             "equal groups")
+
+    def tensors(self):
+        return [TensorDecl(self.name, (self.spec.size,), keep="float32", init="gain")]
+
+    def bind(self, weights):
+        self.gain = weights[self.name]
+
+    def add_normed(self, resid, delta, cast_dtype=None):
+        """resid += norm(delta) * gain; the new residual in ``cast_dtype`` if asked."""
+        return self.ctx.ops.group_norm_add(resid, delta, self.gain, self.spec.groups,
+                                           self.spec.eps, cast_dtype)
+
+    def forward(self, resid, delta, rows=None):
+        if delta is not None:
+            raise ValueError("a grouped norm of the residual stream takes no pending "
+                             "contribution; add it first")
+        return self.ctx.ops.group_norm_rows(resid, rows, self.gain, self.spec.groups,
+                                            self.spec.eps, self.ctx.dtype)
+
+
+register_part("norm", "grouped_rmsnorm", GroupedRmsNorm)

@@ -38,3 +38,43 @@ class RotaryEncoding:
 
 
 register_part("position", "rope", RotaryEncoding)
+
+
+class InterleavedRotary:
+    """Rotation of neighbouring pairs, optionally with YaRN-stretched frequencies.
+
+    ``pair_table()`` gives (frequency per pair as fp32 [rotary_dim/2], factor on cos and
+    sin, rotary_dim).  The frequencies are formed in float64 and rounded once; the
+    kernel multiplies position and frequency, and takes cos and sin, in fp32."""
+
+    def __init__(self, spec, ctx, prefix: str):
+        import math
+        self.spec = spec
+        r = spec.rotary_dim
+        if r % 2 or r > spec.head_dim or r < 0:
+            raise ValueError(f"rotary_dim {r} must be even and at most {spec.head_dim}")
+        i = torch.arange(r // 2, dtype=torch.float64)
+        f = torch.pow(torch.tensor(float(spec.theta), dtype=torch.float64), -2.0 * i / max(r, 1))
+        self.magnitude = 1.0
+        if spec.scaling_factor > 0:
+            def pair_with_turns(turns):
+                return r * math.log(spec.original_context / (2.0 * math.pi * turns)) / (
+                    2.0 * math.log(spec.theta))
+            lo = max(math.floor(pair_with_turns(spec.fast_turns)), 0)
+            hi = min(math.ceil(pair_with_turns(spec.slow_turns)), r - 1)
+            ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            f = f / spec.scaling_factor * ramp + f * (1.0 - ramp)
+            self.magnitude = 0.1 * math.log(spec.scaling_factor) + 1.0
+        self.freq = f.to(torch.float32).to(ctx.device)
+
+    def tensors(self):
+        return []
+
+    def bind(self, weights):
+        pass
+
+    def pair_table(self):
+        return self.freq, self.magnitude, self.spec.rotary_dim
+
+
+register_part("position", "rope_interleaved", InterleavedRotary)

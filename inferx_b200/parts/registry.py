@@ -1,7 +1,8 @@
 """Registry from (role, kind) to the class that runs a spec of that kind.
 
-Roles: ``"norm"``, ``"position"``, ``"mixer"``, ``"feed_forward"`` and ``"block"``
-(the arrangement of one layer's parts).  A new kind
+Roles: ``"norm"``, ``"position"``, ``"mixer"``, ``"feed_forward"``, ``"mixer_input"``
+(a transform of what the mixer reads) and ``"block"`` (the arrangement of one layer's
+parts).  A new kind
 of part is added by registering its class here; nothing else in the package
 names the kinds.
 """
@@ -9,7 +10,7 @@ from __future__ import annotations
 
 from typing import Any, Dict
 
-ROLES = ("norm", "position", "mixer", "feed_forward", "block")
+ROLES = ("norm", "position", "mixer", "feed_forward", "block", "mixer_input")
 _PARTS: Dict[str, Dict[str, type]] = {r: {} for r in ROLES}
 
 

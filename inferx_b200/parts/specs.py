@@ -35,6 +35,80 @@ class RopeSpec:
 
 
 @dataclass(frozen=True)
+class GroupedRmsNormSpec:
+    """RMS norm of ``groups`` equal consecutive parts of a row, each over its own root
+    mean square, then the whole row times the gain."""
+    size: int
+    eps: float
+    groups: int = 1
+    kind: str = "grouped_rmsnorm"
+
+
+@dataclass(frozen=True)
+class InterleavedRopeSpec:
+    """Rotary encoding of neighbouring pairs (2i, 2i+1) of the first ``rotary_dim``
+    entries of a vector of ``head_dim``, frequency ``theta^(-2i/rotary_dim)``.  With
+    ``scaling_factor`` > 0 the frequencies are stretched YaRN-wise: pair i keeps its
+    frequency below ``lo``, has it divided by the factor above ``hi`` and is blended
+    linearly in between, where lo and hi are the pair indices at which the original
+    context ``original_context`` holds ``fast_turns`` and ``slow_turns`` full turns;
+    cos and sin are multiplied by ``0.1 ln(factor) + 1``."""
+    head_dim: int
+    rotary_dim: int
+    theta: float
+    scaling_factor: float = 0.0
+    original_context: float = 0.0
+    fast_turns: float = 32.0
+    slow_turns: float = 1.0
+    kind: str = "rope_interleaved"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Attention whose keys and values are widened from one cached latent per token.
+    Per head: ``dim`` plain and ``rot_dim`` rotated query/key entries, ``vdim`` value
+    entries; the latent has ``kv_rank`` entries and is RMS-normed with ``latent_eps``;
+    one rotated key part of ``rot_dim`` is shared by all heads.  ``output_gate``: the
+    heads' outputs are multiplied by sigmoid(W_g h) before the output projection."""
+    hidden: int
+    heads: int
+    dim: int
+    rot_dim: int
+    vdim: int
+    kv_rank: int
+    scale: float
+    window: int        # keys visible to a query including itself; 0 = all
+    position: Any      # encoding of the rotated part, or None
+    latent_eps: float
+    output_gate: bool = True
+    # tensor names inside the mixer's prefix
+    names: tuple = (("q", "q"), ("dkv", "dkv"), ("dkv_norm", "dkv.norm"), ("uk", "uk"),
+                    ("uv", "uv"), ("g", "g"), ("o", "o"))
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class TokenShiftSpec:
+    """h_t + (h_{t-1} - h_t) * mix per channel, with zeros before a sequence's first
+    token; the previous token's h is per-request state."""
+    size: int
+    kind: str = "token_shift"
+
+
+@dataclass(frozen=True)
+class ClampedGluSpec:
+    """down(min(g, L) * sigmoid(alpha * min(g, L)) * (clamp(u, -L, L) + up_shift)) with
+    g and u the gate and up projections."""
+    hidden: int
+    intermediate: int
+    limit: float
+    alpha: float = 1.702
+    up_shift: float = 1.0
+    names: tuple = ("gate", "up", "down")
+    kind: str = "clamped_glu"
+
+
+@dataclass(frozen=True)
 class AttentionSpec:
     hidden: int
     heads: int
@@ -72,7 +146,9 @@ class MoeSpec:
 @dataclass(frozen=True)
 class LayerSpec:
     """One layer: its parts, and ``kind``, the arrangement they run in.  "pre_norm" is
-    x += mixer(norm(x)); x += ffn(norm(x))."""
+    x += mixer(norm(x)); x += ffn(norm(x)); "sublayer_norm" is x += norm(mixer(x));
+    x += norm(ffn(x)), where ``input_norm`` follows the mixer and ``post_norm`` the
+    feed-forward (``ffn`` and ``post_norm`` may be None: a layer without feed-forward)."""
     prefix: str  # tensor-name prefix, e.g. "model.layers.3"
     input_norm: Any
     mixer: Any
@@ -84,6 +160,9 @@ class LayerSpec:
     post_norm_name: str = "post_attention_layernorm"
     ffn_name: str = "mlp"
     kind: str = "pre_norm"
+    # a transform of what the mixer reads (a token shift, for instance), or None
+    mixer_input: Any = None
+    mixer_input_name: str = "shift"
 
 
 @dataclass(frozen=True)
@@ -116,3 +195,4 @@ class ModelSpec:
     embed_name: str = "model.embed_tokens.weight"
     final_norm_name: str = "model.norm"
     head_name: str = "lm_head.weight"
+    embed_scale: float = 1.0     # the residual stream starts as embed[token] * embed_scale

@@ -16,8 +16,8 @@ def _f(t):
     return t.to(torch.float32)
 
 
-def embed(table, ids, out=None):
-    r = _f(table)[ids.long()]
+def embed(table, ids, out=None, scale=1.0):
+    r = _f(table)[ids.long()] * scale
     if out is not None:
         out.copy_(r)
         return out
@@ -282,3 +282,100 @@ def sample(logits, temperature=None, seeds=None, top_p=None, top_k=None, min_p=N
         out.copy_(ids)
         return out
     return ids
+
+
+# -- parts of decoders that normalise a sublayer's output, shift tokens, gate or clamp ----
+def token_shift(resid, mix, state, step, out_dtype):
+    out = torch.empty_like(resid)
+    cu = [int(v) for v in step.cu_q]
+    for s in range(len(cu) - 1):
+        a, b = cu[s], cu[s + 1]
+        slot = int(step.state_slot[s])
+        prev = torch.cat([state[slot][None, :], resid[a:b - 1]], dim=0)
+        out[a:b] = resid[a:b] + (prev - resid[a:b]) * mix
+        state[slot] = resid[b - 1]
+    return out.to(out_dtype)
+
+
+def _group_norm(v, gain, groups, eps):
+    n, w = v.shape
+    parts = v.reshape(n, groups, w // groups)
+    ms = (parts * parts).sum(-1, keepdim=True) / (w // groups)
+    return (parts * (1.0 / torch.sqrt(ms + eps))).reshape(n, w) * gain
+
+
+def group_norm_add(resid, delta, gain, groups, eps, cast_dtype=None):
+    resid += _group_norm(_f(delta), gain, groups, eps)
+    return resid.to(cast_dtype) if cast_dtype is not None else None
+
+
+def group_norm_rows(resid, rows, gain, groups, eps, out_dtype):
+    v = resid if rows is None else resid[rows.long()]
+    return _group_norm(v, gain, groups, eps).to(out_dtype)
+
+
+def glu_clamped(gu, limit, alpha, up_shift):
+    i = gu.shape[1] // 2
+    g = torch.clamp(_f(gu[:, :i]), max=limit)
+    u = torch.clamp(_f(gu[:, i:]), -limit, limit)
+    return (g / (1.0 + torch.exp(-alpha * g)) * (u + up_shift)).to(gu.dtype)
+
+
+def gate_up_glu_clamped(x, w_gate_up, limit, alpha, up_shift):
+    return glu_clamped(linear(x, w_gate_up), limit, alpha, up_shift)
+
+
+def batched_linear(x, w):
+    return torch.bmm(_f(x), _f(w).transpose(1, 2)).to(x.dtype)
+
+
+def _turn_pairs(v, positions, freq, mag, rot_dims):
+    # v [T, ..., d]: pairs (2i, 2i+1), i < rot_dims / 2, turned by position * freq[i]
+    if not rot_dims:
+        return v
+    shape = [v.shape[0]] + [1] * (v.dim() - 2) + [rot_dims // 2]
+    a = (positions.to(torch.float32)[:, None] * freq[None, :]).reshape(shape)
+    c, s = torch.cos(a) * mag, torch.sin(a) * mag
+    out = v.clone()
+    u, w = v[..., 0:rot_dims:2], v[..., 1:rot_dims:2]
+    out[..., 0:rot_dims:2] = u * c - w * s
+    out[..., 1:rot_dims:2] = w * c + u * s
+    return out
+
+
+def latent_prepare(proj, q_off, kv_off, positions, freq, mag, gain, eps, heads, dim, rot_dim,
+                   rot_dims, rank, cache, slots):
+    T = proj.shape[0]
+    x = _f(proj)
+    if cache is not None:
+        c = x[:, kv_off:kv_off + rank]
+        c = c * (1.0 / torch.sqrt((c * c).sum(-1, keepdim=True) / rank + eps)) * gain
+        kr = _turn_pairs(x[:, kv_off + rank:kv_off + rank + rot_dim], positions, freq, mag,
+                         rot_dims)
+        _scatter(cache, torch.cat([c, kr], dim=-1)[:, None, :], slots)
+    q = x[:, q_off:q_off + heads * (dim + rot_dim)].reshape(T, heads, dim + rot_dim)
+    return _turn_pairs(q[..., dim:], positions, freq, mag, rot_dims).contiguous().to(proj.dtype)
+
+
+def latent_attention(q_lat, q_rot, cache, block_table, step, window, scale):
+    H, T, rank = q_lat.shape
+    page = cache.shape[2]
+    out = torch.zeros(H, T, rank, dtype=torch.float32)
+    for t in range(T):
+        s, pos = int(step.seq_of_token[t]), int(step.positions[t])
+        start = max(0, pos - window + 1) if window > 0 else 0
+        kp = torch.arange(start, pos + 1)
+        pages = block_table[s][(kp // page).long()].long()
+        assert (pages >= 0).all(), "attention reads a page that was given back"
+        rec = _f(cache[pages, 0, (kp % page).long(), :])
+        q = torch.cat([_f(q_lat[:, t]), _f(q_rot[t])], dim=-1)       # [H, rank + rot]
+        sc = (q @ rec.T) * scale
+        p = torch.exp(sc - sc.max(dim=-1, keepdim=True).values)
+        out[:, t] = (p @ rec[:, :rank]) / p.sum(-1, keepdim=True)
+    return out.to(q_lat.dtype)
+
+
+def gate_heads(o, proj, gate_off):
+    H, T, D = o.shape
+    g = _f(proj[:, gate_off:gate_off + H * D])
+    return (_f(o).transpose(0, 1).reshape(T, H * D) / (1.0 + torch.exp(-g))).to(o.dtype)
