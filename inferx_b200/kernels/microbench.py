@@ -8,6 +8,8 @@
     python -m inferx_b200.kernels.microbench router --tokens 2048
     python -m inferx_b200.kernels.microbench qkv --rows 8 [--separate]
     python -m inferx_b200.kernels.microbench grouped --tokens 2048
+    python -m inferx_b200.kernels.microbench latent_attn --tokens 2048 --rank 512 --rot-dim 64 [--form mma|general]
+    python -m inferx_b200.kernels.microbench latent_attn --tokens 1 --batch 8 --context 4096
 
 Each case runs one kernel face at Qwen1.5-MoE-A2.7B sizes (or the sizes given),
 cycling through enough copies of its inputs that consecutive iterations do not
@@ -225,10 +227,57 @@ def attn_prefill(args):
             "us": round(us, 2), "TFLOPs": round(flops / us / 1e6, 1)}
 
 
+def latent_attn(args):
+    """Attention over cached latent records: ``--tokens`` > 1 is one prompt of that many
+    tokens; ``--tokens 1`` is ``--batch`` sequences of ``--context`` tokens bringing one
+    token each.  FLOP = 2 * (2 * rank + rot) per (query row, visible key)."""
+    from . import ops
+    T, H, rank, dr, page, W = args.tokens, args.heads, args.rank, args.rot_dim, args.page, \
+        args.window
+    dt = torch.float32 if args.dtype == "float32" else torch.bfloat16
+    decode = T == 1
+    S = args.batch if decode else 1
+    C = args.context if decode else max(args.context if args.context_given else T, T)
+    pages_per_seq = -(-C // page)
+    P = S * pages_per_seq
+    per_copy = P * page * (rank + dr) * 2
+    n = min(_copies(per_copy), 8) if decode else 1
+    caches = [torch.randn(P, 1, page, rank + dr, device="cuda", dtype=dt) * 0.3 for _ in range(n)]
+    bt = torch.randperm(P, device="cuda").to(torch.int32).view(S, pages_per_seq)
+    rows = S * T
+    q_lat = torch.randn(H, rows, rank, device="cuda", dtype=dt) * 0.3
+    q_rot = torch.randn(rows, H, dr, device="cuda", dtype=dt) * 0.3
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    step = types.SimpleNamespace(
+        seq_of_token=i32([s for s in range(S) for _ in range(T)]),
+        positions=i32([C - T + t for _ in range(S) for t in range(T)]),
+        cu_q=i32([s * T for s in range(S + 1)]), q_pos0=i32([C - T] * S), q_lens=[T] * S)
+    scale = 1.0 / math.sqrt(rank)
+
+    def fn(i):
+        ops.latent_attention(q_lat, q_rot, caches[i], bt, step, W, scale,
+                             kernel=args.form or None)
+    us = _time(fn, n, args.iters)
+    pairs = 0
+    for t in range(T):
+        pos = C - T + t
+        pairs += min(pos + 1, W) if W else pos + 1
+    pairs *= S * H
+    flops = 2 * (2 * rank + dr) * pairs
+    span = min(C, W + T - 1) if W else C
+    nbytes = S * span * (rank + dr) * caches[0].element_size()
+    return {"case": "latent_attn", "tokens": T, "batch": S, "context": C, "heads": H,
+            "rank": rank, "rot_dim": dr, "window": W, "form": args.form or "auto",
+            "us": round(us, 2), "TFLOPs": round(flops / us / 1e6, 2), "cache_bytes": nbytes,
+            "GBps": round(nbytes / us / 1e3, 1)}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("case", choices=["attn_decode", "grouped", "dense", "attn_prefill", "router",
-                                     "qkv"])
+                                     "qkv", "latent_attn"])
+    ap.add_argument("--rank", type=int, default=512, help="latent_attn: entries of the latent")
+    ap.add_argument("--rot-dim", type=int, default=64, help="latent_attn: rotated key entries")
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)

@@ -1116,15 +1116,41 @@ def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int, positions: torch
     return q_rot
 
 
+# Latent attention forms: "mma" (mma.sync tensor cores; bf16, latent sizes 64 / 128 / 256 /
+# 512, rotated part a multiple of 16) and "general" (CUDA cores in fp32; any sizes, either
+# element type).  Which one runs depends on the model's sizes and element type only,
+# never on the batch, so a position's result does not change with its neighbours.
+USE_MMA_LATENT_ATTENTION = True
+
+
+def check_latent_attention_limits(rank: int, rot_dim: int, where: str = ""):
+    most = _lib().ix_latent_attention_max_rank()
+    if rank > most:
+        raise KernelError(f"{where}: latent size {rank} exceeds the largest the attention "
+                          f"kernels take ({most})")
+    if (rank + rot_dim) * 41 * 4 > 200 * 1024 and not _lib().ix_latent_attention_mma_applies(
+            rank, rot_dim):
+        raise KernelError(f"{where}: records of {rank} + {rot_dim} entries do not fit the "
+                          "general attention kernel's shared memory")
+
+
+def _mma_latent_applies(q_lat, q_rot) -> bool:
+    return bool(q_lat.dtype == torch.bfloat16 and q_lat.is_cuda
+                and _lib().ix_latent_attention_mma_applies(q_lat.shape[2], q_rot.shape[2]))
+
+
 def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, cache: torch.Tensor,
-                     block_table: torch.Tensor, step, window: int, scale: float):
+                     block_table: torch.Tensor, step, window: int, scale: float,
+                     kernel: Optional[str] = None):
     """Attention of this step's queries over cached latent records.
 
     ``q_lat`` [heads, T, rank] (the query with the key matrix folded in), ``q_rot``
     [T, heads, rot_dim], ``cache`` [pages, 1, page, rank + rot_dim].  Scores are
     (q_lat . latent + q_rot . key_rot) * scale over the keys a position sees (itself and
     the ``window`` - 1 before it; all earlier ones when ``window`` is 0); returns
-    sum_j p_j latent_j as [heads, T, rank]."""
+    sum_j p_j latent_j as [heads, T, rank].  ``step`` carries ``seq_of_token``,
+    ``positions``, ``cu_q``, ``q_pos0`` and the host list ``q_lens``.  ``kernel`` picks a
+    form ("mma", "general"); None takes the tensor-core form where it applies."""
     _chk("q_lat", q_lat)
     _chk("q_rot", q_rot, q_lat.dtype)
     _chk("cache", cache, q_lat.dtype)
@@ -1134,7 +1160,28 @@ def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, cache: torch.Tens
     P, one, page, dk = cache.shape
     if one != 1 or dk != rank + dr or q_rot.shape[:2] != (T, H):
         raise KernelError("latent_attention: queries and cache records disagree")
+    if kernel is None:
+        kernel = "mma" if USE_MMA_LATENT_ATTENTION and _mma_latent_applies(q_lat, q_rot) \
+            else "general"
+    if kernel not in ("mma", "general"):
+        raise KernelError(f"latent_attention: no kernel form {kernel!r}")
     out = torch.empty((H, T, rank), dtype=q_lat.dtype, device=q_lat.device)
+    if kernel == "mma":
+        if not _mma_latent_applies(q_lat, q_rot):
+            raise KernelError("latent_attention: the tensor-core form takes bf16, a latent of "
+                              f"64, 128, 256 or 512 and a rotated part in sixteens (got "
+                              f"{q_lat.dtype}, {rank}, {dr})")
+        tpt = _lib().ix_latent_attention_mma_tokens_per_tile(H)
+        tiles = sum(-(-int(n) // tpt) for n in step.q_lens)
+        S = len(step.q_lens)
+        _check(_lib().ix_latent_attention_mma(
+            _ptr(q_lat), ctypes.c_longlong(T * rank), ctypes.c_longlong(rank), _ptr(q_rot),
+            _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(step.cu_q),
+            _ptr(step.q_pos0), S, _ptr(out), ctypes.c_longlong(T * rank),
+            ctypes.c_longlong(rank), H, rank, dr, page, window, ctypes.c_float(scale), tiles,
+            _stream()), "latent_attention (mma)")
+        _count()
+        return out
     _check(_lib().ix_latent_attention(
         _ptr(q_lat), ctypes.c_longlong(T * rank), ctypes.c_longlong(rank), _ptr(q_rot),
         _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(step.seq_of_token),

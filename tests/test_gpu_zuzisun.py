@@ -44,11 +44,13 @@ def _step(q_lens, starts, slots=None):
         cu.append(cu[-1] + n)
     i32 = lambda v: torch.tensor(v, dtype=torch.int32)
     return SimpleNamespace(seq_of_token=i32(seq_of), positions=i32(pos), cu_q=i32(cu),
+                           q_pos0=i32(list(starts)), q_lens=list(q_lens),
                            state_slot=i32(slots if slots is not None else list(range(len(q_lens)))))
 
 
 def _cuda(ns):
-    return SimpleNamespace(**{k: v.cuda() for k, v in vars(ns).items()})
+    return SimpleNamespace(**{k: (v.cuda() if torch.is_tensor(v) else v)
+                              for k, v in vars(ns).items()})
 
 
 # -- kernels alone -------------------------------------------------------------------
@@ -176,15 +178,23 @@ def _attention_case(seed, H, rank, dr, page, q_lens, starts, dtype, spread=1.0):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,rank,dr,page,window", [(3, 40, 16, 4, 10), (5, 48, 8, 8, 0),
                                                    (16, 256, 32, 16, 100), (8, 128, 32, 16, 136),
-                                                   (1, 7, 6, 16, 3), (9, 160, 0, 32, 50)])
+                                                   (1, 7, 6, 16, 3), (9, 160, 0, 32, 50),
+                                                   (70, 64, 16, 8, 33), (5, 512, 64, 16, 0),
+                                                   (64, 128, 0, 16, 77)])
 def test_latent_attention_unequal_batch(dtype, H, rank, dr, page, window):
-    """Single tokens far into their sequences beside portions that start anywhere."""
+    """Single tokens far into their sequences beside portions that start anywhere; every
+    kernel form that takes the sizes."""
     step, bt, cache, q_lat, q_rot = _attention_case(
         rank, H, rank, dr, page, [1, 1, 37, 2, 64, 5], [333, 0, 0, 129, 70, 15], dtype, 0.5)
     ref = host_ops.latent_attention(q_lat, q_rot, cache, bt, step, window, 0.2)
-    out = _ops().latent_attention(q_lat.cuda(), q_rot.cuda(), cache.cuda(), bt.cuda(),
-                                  _cuda(step), window, 0.2)
-    torch.testing.assert_close(out.cpu().float(), ref.float(), **_tol(dtype))
+    forms = ["general"]
+    if dtype == torch.bfloat16 and rank in (64, 128, 256, 512) and dr % 16 == 0:
+        forms.append("mma")
+        assert _ops()._mma_latent_applies(q_lat.cuda(), q_rot.cuda())
+    for form in forms:
+        out = _ops().latent_attention(q_lat.cuda(), q_rot.cuda(), cache.cuda(), bt.cuda(),
+                                      _cuda(step), window, 0.2, kernel=form)
+        torch.testing.assert_close(out.cpu().float(), ref.float(), **_tol(dtype))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -194,8 +204,9 @@ def test_latent_attention_finds_one_key(dtype, page, decode):
     """One key carries a score far above the rest and a latent of fives; the output is
     fives exactly when that key is visible: far back among hundreds, on either side of a
     page border, the oldest key of the window and the one just outside it, position 0."""
-    H, rank, dr, window, scale = 2, 24, 8, 150, 0.5
+    H, rank, dr, window, scale = 2, 64, 16, 150, 0.5
     query_pos = 700
+    forms = ["general", "mma"] if dtype == torch.bfloat16 else ["general"]
     for key_pos, seen in [(700 - 149, True), (700 - 150, False), (0, False), (700, True),
                           (699, True), (16 * 40 - 1, True), (16 * 40, True)]:
         q_lens, starts = ([1], [query_pos]) if decode else ([9], [query_pos - 8])
@@ -207,11 +218,12 @@ def test_latent_attention_finds_one_key(dtype, page, decode):
         rec[rank:] = (qv * (40.0 / scale) / (qv * qv).sum()).to(dtype)
         rec[:rank] = 5.0
         ref = host_ops.latent_attention(q_lat, q_rot, cache, bt, step, window, scale)
-        out = _ops().latent_attention(q_lat.cuda(), q_rot.cuda(), cache.cuda(), bt.cuda(),
-                                      _cuda(step), window, scale).cpu().float()
-        torch.testing.assert_close(out, ref.float(), **_tol(dtype))
-        last = out[:, -1]
-        assert (last.mean() > 4.5) == seen, (key_pos, float(last.mean()))
+        for form in forms:
+            out = _ops().latent_attention(q_lat.cuda(), q_rot.cuda(), cache.cuda(), bt.cuda(),
+                                          _cuda(step), window, scale, kernel=form).cpu().float()
+            torch.testing.assert_close(out, ref.float(), **_tol(dtype))
+            last = out[:, -1]
+            assert (last.mean() > 4.5) == seen, (form, key_pos, float(last.mean()))
     # no window: position 0 is seen from anywhere
     step, bt, cache, q_lat, q_rot = _attention_case(3, H, rank, dr, page, [1], [query_pos], dtype,
                                                     0.1)
@@ -228,16 +240,18 @@ def test_latent_attention_finds_one_key(dtype, page, decode):
 def test_latent_attention_row_does_not_depend_on_its_batch():
     """The same query over the same keys gives the same bits alone, after other
     sequences, and as the last token of a portion."""
-    H, rank, dr, page = 4, 40, 16, 8
-    step, bt, cache, q_lat, q_rot = _attention_case(9, H, rank, dr, page, [1, 6, 1], [50, 200, 90],
-                                                    torch.bfloat16, 0.5)
     ops = _ops()
-    full = ops.latent_attention(q_lat.cuda(), q_rot.cuda(), cache.cuda(), bt.cuda(), _cuda(step),
-                                20, 0.3)
-    alone = _step([1], [205])
-    one = ops.latent_attention(q_lat[:, 6:7].contiguous().cuda(), q_rot[6:7].contiguous().cuda(),
-                               cache.cuda(), bt[1:2].contiguous().cuda(), _cuda(alone), 20, 0.3)
-    assert torch.equal(full[:, 6], one[:, 0])
+    for (H, rank, dr, page), form in (((4, 40, 16, 8), "general"), ((4, 128, 16, 8), "general"),
+                                      ((4, 128, 16, 8), "mma"), ((20, 256, 32, 16), "mma")):
+        step, bt, cache, q_lat, q_rot = _attention_case(9, H, rank, dr, page, [1, 6, 1],
+                                                        [50, 200, 90], torch.bfloat16, 0.5)
+        full = ops.latent_attention(q_lat.cuda(), q_rot.cuda(), cache.cuda(), bt.cuda(),
+                                    _cuda(step), 20, 0.3, kernel=form)
+        alone = _step([1], [205])
+        one = ops.latent_attention(q_lat[:, 6:7].contiguous().cuda(),
+                                   q_rot[6:7].contiguous().cuda(), cache.cuda(),
+                                   bt[1:2].contiguous().cuda(), _cuda(alone), 20, 0.3, kernel=form)
+        assert torch.equal(full[:, 6], one[:, 0]), (H, rank, form)
 
 
 # -- the engine against the plain model ------------------------------------------------
