@@ -1171,15 +1171,30 @@ def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, cache: torch.Tens
             raise KernelError("latent_attention: the tensor-core form takes bf16, a latent of "
                               f"64, 128, 256 or 512 and a rotated part in sixteens (got "
                               f"{q_lat.dtype}, {rank}, {dr})")
-        tpt = _lib().ix_latent_attention_mma_tokens_per_tile(H)
+        lib = _lib()
+        # blocks of 64 (token, head) rows; of 16 where every sequence brings one token and
+        # the heads would leave most of 64 rows empty
+        rows = 16 if (max(step.q_lens) == 1 and H % 64 and H % 64 <= 32) else 64
+        tpt = lib.ix_latent_attention_mma_tokens_per_tile(H, rows)
         tiles = sum(-(-int(n) // tpt) for n in step.q_lens)
         S = len(step.q_lens)
-        _check(_lib().ix_latent_attention_mma(
+        # few blocks over long runs of keys: the keys are cut into chunks, merged afterwards
+        max_kv = int(getattr(step, "max_kv_len", 0) or block_table.shape[1] * page)
+        span = min(window + tpt - 1, max_kv) if window > 0 else max_kv
+        ct = ctypes.c_int(0)
+        nchunks = lib.ix_latent_attention_mma_chunks(tiles * -(-H // rows), span, ctypes.byref(ct))
+        part_o = part_ml = None
+        if ct.value > 0:
+            part_o = torch.empty((T, H, nchunks, rank), dtype=torch.float32, device=q_lat.device)
+            part_ml = torch.empty((T, H, nchunks, 2), dtype=torch.float32, device=q_lat.device)
+        _check(lib.ix_latent_attention_mma(
             _ptr(q_lat), ctypes.c_longlong(T * rank), ctypes.c_longlong(rank), _ptr(q_rot),
             _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(step.cu_q),
             _ptr(step.q_pos0), S, _ptr(out), ctypes.c_longlong(T * rank),
-            ctypes.c_longlong(rank), H, rank, dr, page, window, ctypes.c_float(scale), tiles,
-            _stream()), "latent_attention (mma)")
+            ctypes.c_longlong(rank), T, H, rank, dr, page, window, ctypes.c_float(scale), tiles,
+            rows, ct.value, nchunks, _ptr(part_o), _ptr(part_ml), _stream()), "latent_attention (mma)")
+        if ct.value > 0:
+            _count()
         _count()
         return out
     _check(_lib().ix_latent_attention(

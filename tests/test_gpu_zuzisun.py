@@ -237,6 +237,22 @@ def test_latent_attention_finds_one_key(dtype, page, decode):
     assert out.mean() > 4.5
 
 
+@pytest.mark.parametrize("window", [0, 1500])
+@pytest.mark.parametrize("H,rank,dr", [(16, 512, 64), (8, 128, 32), (70, 64, 16)])
+def test_latent_attention_single_tokens_over_long_contexts(window, H, rank, dr):
+    """A few single tokens late in long sequences: the tensor-core form cuts the keys into
+    chunks and merges the partial results."""
+    dtype = torch.bfloat16
+    step, bt, cache, q_lat, q_rot = _attention_case(5, H, rank, dr, 16, [1, 1, 1],
+                                                    [2999, 37, 1700], dtype, 0.3)
+    step.max_kv_len = 3000
+    ref = host_ops.latent_attention(q_lat, q_rot, cache, bt, step, window, 0.1)
+    for form in ("general", "mma"):
+        out = _ops().latent_attention(q_lat.cuda(), q_rot.cuda(), cache.cuda(), bt.cuda(),
+                                      _cuda(step), window, 0.1, kernel=form)
+        torch.testing.assert_close(out.cpu().float(), ref.float(), **_tol(dtype))
+
+
 def test_latent_attention_row_does_not_depend_on_its_batch():
     """The same query over the same keys gives the same bits alone, after other
     sequences, and as the last token of a portion."""
