@@ -759,6 +759,83 @@ def serving_check(args):
     return 0 if ok else 1
 
 
+# ---------------------------------------------------------------------------
+# `--designs`: the Zuzisun design (latent attention, token shift, sublayer norms, clamped
+# GLU) beside the closest model this engine already had, Qwen2-MoE with every layer dense,
+# at equal width, depth, heads, feed-forward width, window and vocabulary.  Random weights.
+DESIGN_SIZES = {
+    # name: width, heads, plain/rotated/value entries per head, latent, ff, window, twin kv heads
+    "1k": dict(width=1024, heads=8, dim=64, rot=32, vdim=64, rank=256, ff=2816, window=1024,
+               twin_head=64, twin_kv=8),
+    "2k": dict(width=2048, heads=16, dim=128, rot=64, vdim=128, rank=512, ff=5632, window=4096,
+               twin_head=128, twin_kv=16),
+    "4k": dict(width=4096, heads=32, dim=128, rot=64, vdim=128, rank=512, ff=11008, window=4096,
+               twin_head=128, twin_kv=8),
+}
+DESIGN_VOCAB = 32000
+
+
+def design_configs(z, layers):
+    import math
+    mixer = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"],
+             "kv_rank": z["rank"], "scale": 1.0 / math.sqrt(z["dim"] + z["rot"]),
+             "mask": {"size": z["window"]},
+             "rot": {"base": 1000000.0, "dims": z["rot"],
+                     "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    new = {"architecture": "Zuzisun", "vocab": DESIGN_VOCAB, "width": z["width"],
+           "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5, "groups": 4},
+           "layers": [{"type": "latent_attention", "mixer": mixer,
+                       "mlp": {"kind": "dense", "ff": z["ff"], "limit": 7.0}}] * layers}
+    twin = {"architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",
+            "num_hidden_layers": layers, "hidden_size": z["width"],
+            "num_attention_heads": z["heads"], "num_key_value_heads": z["twin_kv"],
+            "head_dim": z["twin_head"], "num_experts": 1, "num_experts_per_tok": 1,
+            "moe_intermediate_size": 64, "shared_expert_intermediate_size": 0,
+            "intermediate_size": z["ff"], "decoder_sparse_step": 1,
+            "mlp_only_layers": list(range(layers)), "norm_topk_prob": False,
+            "vocab_size": DESIGN_VOCAB, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+            "use_sliding_window": True, "sliding_window": z["window"], "max_window_layers": 0,
+            "tie_word_embeddings": True, "torch_dtype": "bfloat16"}
+    return new, twin
+
+
+def designs(args):
+    """One JSON line per size: prompt tokens/s (one prompt of --prefill-tokens, default
+    2048) and decode tokens/s (--batch sequences at --context) of both designs, device
+    time by CUDA events after warm-up; each step's weights and cache exceed the L2."""
+    import torch
+    layers = args.layers or 4
+    prompt = args.prefill_tokens or 2048
+    B = args.batch
+    for name in (args.design_sizes.split(",") if args.design_sizes else list(DESIGN_SIZES)):
+        z = DESIGN_SIZES[name]
+        C = args.context or 4096
+        row = {"size": name, "layers": layers, "width": z["width"], "heads": z["heads"],
+               "ff": z["ff"], "window": z["window"], "prompt_tokens": prompt, "batch": B,
+               "context": C, "dtype": "bf16", "data": "synthetic, random weights"}
+        for label, cfg in zip(("zuzisun", "qwen2_dense"), design_configs(z, layers)):
+            extra = args.steps + args.warmup + 8
+            rt = make_runtime(cfg, max(B, 1), max(C + extra, prompt) + 64, 0,
+                              use_graphs=not args.no_graphs, max_slots=B + 1)
+            ms = time_prefill(rt, prompt, reps=5, warmup=3)
+            dec = time_decode(rt, B, C, args.steps, args.warmup)
+            row[label] = {"prefill_ms": round(ms, 3), "prefill_tok_s": round(prompt / ms * 1e3, 1),
+                          "decode_ms_per_step": round(dec["ms_per_step"], 4),
+                          "decode_tok_s": round(dec["tok_s"], 1),
+                          "launches_per_decode_step": dec["launches"] // max(1, args.steps),
+                          "cache_bytes_per_token": sum(
+                              n.bytes_per_token(torch.bfloat16) for needs in rt.model.cache_needs()
+                              for n in needs if hasattr(n, "bytes_per_token"))}
+            del rt
+            torch.cuda.empty_cache()
+        row["prefill_ratio"] = round(row["zuzisun"]["prefill_tok_s"]
+                                     / row["qwen2_dense"]["prefill_tok_s"], 3)
+        row["decode_ratio"] = round(row["zuzisun"]["decode_tok_s"]
+                                    / row["qwen2_dense"]["decode_tok_s"], 3)
+        print(json.dumps(row), flush=True)
+    return 0
+
+
 def reference_arm():
     why = ("divedb/InferX is a C++20/CMake project with no Python package (no setup.py or "
            "pyproject.toml) and needs abseil, CLI11, folly and FlashInfer sources that are absent "
@@ -796,9 +873,17 @@ def main(argv=None):
                     help="print what each kernel face adds to the recorded decode step")
     ap.add_argument("--prefill-tokens", type=int, default=0,
                     help="with --marginal: a prompt step of this many tokens instead")
+    ap.add_argument("--designs", action="store_true",
+                    help="prompt and decode throughput of the Zuzisun design beside Qwen2-MoE "
+                         "with dense layers at equal sizes (random weights); --layers (4), "
+                         "--batch, --context (4096), --prefill-tokens (2048) apply")
+    ap.add_argument("--design-sizes", default="", help="with --designs: of 1k,2k,4k (all)")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return reference_arm()
+    if args.designs:
+        args.warmup = max(args.warmup, 3)
+        return designs(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

@@ -5,6 +5,8 @@
 //
 //   out[r, j] = sum_k x[src(r), k] * w[e(r), j, k]          (plain)
 //   out[r, j] = silu(x . wg[e, j]) * (x . wu[e, j])          (DUAL: SwiGLU fused)
+//   out[r, j] = g' * sigmoid(a g') * (clamp(u, -L, L) + b), g' = min(g, L), with g and u
+//               the two products above                       (DUAL with a limit L > 0)
 //
 // Groups are the experts of a mixture (ragged row ranges from `offsets`, source
 // rows from `rows`: the reference's GatherRows + GroupedGemmBf16Kernel<1> decode
@@ -47,12 +49,24 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, unsigned a0, unsigned a
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+struct DualAct {     // the gated unit's form; limit <= 0: silu(g) * u
+  float limit, alpha, shift;
+};
+__device__ __forceinline__ float dual_act(float g, float u, const DualAct& a) {
+  if (a.limit > 0.f) {
+    g = fminf(g, a.limit);
+    u = fminf(fmaxf(u, -a.limit), a.limit);
+    return g / (1.0f + __expf(-a.alpha * g)) * (u + a.shift);
+  }
+  return g / (1.0f + __expf(-g)) * u;
+}
+
 template <typename TO, bool DUAL, int NT, int KSPLIT>
 __global__ void __launch_bounds__(SM_THREADS, (NT >= 4 || (NT >= 2 && KSPLIT == 1)) ? 1 : 2)
 gemm_small_m_kernel(const bf16* __restrict__ x, const int* __restrict__ rows,
                     const int* __restrict__ offsets, const bf16* __restrict__ w,
                     TO* __restrict__ out, int M_single, int N, int K, long long w_expert_stride,
-                    int offsets_settled) {
+                    int offsets_settled, DualAct act) {
   constexpr int TILES = SM_WARPS / KSPLIT;        // 16-column tiles per block
   // k-steps kept in flight per warp: deep when a warp streams all of K for its tile,
   // shallower when K is split over warps (more warps resident instead)
@@ -172,7 +186,7 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const int* __restrict__ rows,
           const int r = r0 + i * 8 + 2 * t + (c & 1);
           if (j < N && r < hi) {
             float v = acc[i][c];
-            if (DUAL) v = v / (1.0f + __expf(-v)) * acc2[i][c];
+            if (DUAL) v = dual_act(v, acc2[i][c], act);
             out[(size_t)r * N + j] = from_f32<TO>(v);
           }
         }
@@ -198,7 +212,7 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const int* __restrict__ rows,
         const int j = (blockIdx.x * TILES + ti) * 16 + ((c & 2) ? gg + 8 : gg);
         const int r = r0 + i * 8 + 2 * tt + (c & 1);
         if (j < N && r < hi) {
-          if (DUAL) v = v / (1.0f + __expf(-v)) * v2;
+          if (DUAL) v = dual_act(v, v2, act);
           out[(size_t)r * N + j] = from_f32<TO>(v);
         }
       }
@@ -208,7 +222,7 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const int* __restrict__ rows,
 
 template <typename TO, bool DUAL, int NT, int KSPLIT>
 static int launch_small_m2(const void* x, const int* rows, const int* offsets, const void* w,
-                           void* out, int M, int N, int K, int E, int settled,
+                           void* out, int M, int N, int K, int E, int settled, DualAct act,
                            cudaStream_t stream) {
   if (E > 65535) return IX_ERR_SIZE;
   const long long w_rows = DUAL ? 2LL * N : N;
@@ -216,25 +230,25 @@ static int launch_small_m2(const void* x, const int* rows, const int* offsets, c
   dim3 grid((N + 16 * TILES - 1) / (16 * TILES), E);
   ix_launch(gemm_small_m_kernel<TO, DUAL, NT, KSPLIT>, grid, dim3(SM_THREADS), 0, stream,
             (const bf16*)x, rows, offsets, (const bf16*)w, (TO*)out, offsets ? 0 : M, N, K,
-            w_rows * K, settled);
+            w_rows * K, settled, act);
   return ix_launch_status();
 }
 
 template <typename TO, bool DUAL, int NT>
 static int launch_small_m(const void* x, const int* rows, const int* offsets, const void* w,
                           void* out, int M, int N, int K, int E, int active_groups, int settled,
-                          cudaStream_t stream) {
+                          DualAct act, cudaStream_t stream) {
   // enough warps to keep every SM streaming: split K over warps when there are few tiles
   const long long tiles = (long long)((N + 15) / 16) * (active_groups > 0 ? active_groups : 1);
   int ksplit = 1;
   while (ksplit < 8 && tiles * ksplit < 148 * 8) ksplit *= 2;
   if (ksplit == 1)
-    return launch_small_m2<TO, DUAL, NT, 1>(x, rows, offsets, w, out, M, N, K, E, settled, stream);
+    return launch_small_m2<TO, DUAL, NT, 1>(x, rows, offsets, w, out, M, N, K, E, settled, act, stream);
   if (ksplit == 2)
-    return launch_small_m2<TO, DUAL, NT, 2>(x, rows, offsets, w, out, M, N, K, E, settled, stream);
+    return launch_small_m2<TO, DUAL, NT, 2>(x, rows, offsets, w, out, M, N, K, E, settled, act, stream);
   if (ksplit == 4)
-    return launch_small_m2<TO, DUAL, NT, 4>(x, rows, offsets, w, out, M, N, K, E, settled, stream);
-  return launch_small_m2<TO, DUAL, NT, 8>(x, rows, offsets, w, out, M, N, K, E, settled, stream);
+    return launch_small_m2<TO, DUAL, NT, 4>(x, rows, offsets, w, out, M, N, K, E, settled, act, stream);
+  return launch_small_m2<TO, DUAL, NT, 8>(x, rows, offsets, w, out, M, N, K, E, settled, act, stream);
 }
 
 // x: [*, K] bf16; w: [E, N (or 2N when dual), K] bf16; out: [rows, N] bf16 or fp32.
@@ -243,10 +257,14 @@ static int launch_small_m(const void* x, const int* rows, const int* offsets, co
 // groups are expected to have rows (a hint for how to spread the work; 0 = all).
 // offsets_settled: nonzero when `offsets` was written at least two launches back in the
 // stream, which lets a grouped launch start its weight stream before its wait.
-IX_API int ix_gemm_small_m(const void* x, const int* rows, const int* offsets, const void* w,
-                           void* out, int out_dtype, int dual, int M, int N, int K, int E,
-                           int rows_per_pass, int active_groups, int offsets_settled,
-                           cudaStream_t stream) {
+// act_limit > 0 (dual only): the clamped gated unit with that limit, sigmoid slope
+// act_alpha and act_shift added to the clamped linear branch; otherwise silu(g) * u.
+IX_API int ix_gemm_small_m_act(const void* x, const int* rows, const int* offsets, const void* w,
+                               void* out, int out_dtype, int dual, int M, int N, int K, int E,
+                               int rows_per_pass, int active_groups, int offsets_settled,
+                               float act_limit, float act_alpha, float act_shift,
+                               cudaStream_t stream) {
+  const DualAct act = {act_limit, act_alpha, act_shift};
   if (N <= 0 || K <= 0 || E <= 0) return IX_ERR_SIZE;
   if (K % 8 != 0) return IX_ERR_UNSUPPORTED;
   if (!offsets && E != 1) return IX_ERR_SIZE;
@@ -256,9 +274,9 @@ IX_API int ix_gemm_small_m(const void* x, const int* rows, const int* offsets, c
   if (active_groups <= 0 || active_groups > E) active_groups = E;
 #define IX_SM(TO, D)                                                                          \
   do {                                                                                        \
-    if (nt == 4) return launch_small_m<TO, D, 4>(x, rows, offsets, w, out, M, N, K, E, active_groups, offsets_settled, stream); \
-    if (nt == 2) return launch_small_m<TO, D, 2>(x, rows, offsets, w, out, M, N, K, E, active_groups, offsets_settled, stream); \
-    return launch_small_m<TO, D, 1>(x, rows, offsets, w, out, M, N, K, E, active_groups, offsets_settled, stream); \
+    if (nt == 4) return launch_small_m<TO, D, 4>(x, rows, offsets, w, out, M, N, K, E, active_groups, offsets_settled, act, stream); \
+    if (nt == 2) return launch_small_m<TO, D, 2>(x, rows, offsets, w, out, M, N, K, E, active_groups, offsets_settled, act, stream); \
+    return launch_small_m<TO, D, 1>(x, rows, offsets, w, out, M, N, K, E, active_groups, offsets_settled, act, stream); \
   } while (0)
   if (out_dtype == IX_BF16) {
     if (dual) IX_SM(bf16, true);
@@ -270,4 +288,12 @@ IX_API int ix_gemm_small_m(const void* x, const int* rows, const int* offsets, c
   }
 #undef IX_SM
   return IX_ERR_DTYPE;
+}
+
+IX_API int ix_gemm_small_m(const void* x, const int* rows, const int* offsets, const void* w,
+                           void* out, int out_dtype, int dual, int M, int N, int K, int E,
+                           int rows_per_pass, int active_groups, int offsets_settled,
+                           cudaStream_t stream) {
+  return ix_gemm_small_m_act(x, rows, offsets, w, out, out_dtype, dual, M, N, K, E, rows_per_pass,
+                             active_groups, offsets_settled, 0.f, 1.f, 0.f, stream);
 }

@@ -11,7 +11,8 @@
 //   ix_latent_prepare    per token: RMS norm of the latent (fp32), interleaved rotation
 //                        of the shared key part and of every head's rotated query
 //                        part (angles, cos and sin in fp32), record written into its
-//                        cache slot
+//                        cache slot; the plain query parts laid out heads outermost
+//                        for the product with the folded key matrix
 //   ix_latent_attention  general kernel: any sizes, fp32 arithmetic, either element
 //                        type; one warp per (token, head), keys in tiles of 32 that
 //                        start on multiples of 32 of the absolute position, so that a
@@ -30,8 +31,8 @@ __global__ void latent_prepare_kernel(const TA* __restrict__ proj, long long ld,
                                       const float* __restrict__ freq, float mag,
                                       const float* __restrict__ gain, float eps,
                                       const int* __restrict__ slots, TA* __restrict__ cache,
-                                      TA* __restrict__ q_rot, int H, int dn, int dr, int rot_dims,
-                                      int rank) {
+                                      TA* __restrict__ q_rot, TA* __restrict__ q_plain, int T, int H,
+                                      int dn, int dr, int rot_dims, int rank) {
   __shared__ float scratch[32];
   IX_PDL_WAIT();
   const int t = blockIdx.x;
@@ -63,6 +64,11 @@ __global__ void latent_prepare_kernel(const TA* __restrict__ proj, long long ld,
       if (2 * p + 1 < dr) rec[rank + 2 * p + 1] = from_f32<TA>(b);
     }
   }
+  // the plain query parts, heads outermost: [H, T, dn]
+  for (int idx = threadIdx.x; idx < H * dn; idx += blockDim.x) {
+    const int h = idx / dn, d = idx - h * dn;
+    q_plain[((size_t)h * T + t) * dn + d] = row[q_off + (size_t)h * (dn + dr) + d];
+  }
   const int pairs = (dr + 1) / 2;
   for (int idx = threadIdx.x; idx < H * pairs; idx += blockDim.x) {
     const int h = idx / pairs, p = idx - h * pairs;
@@ -85,8 +91,8 @@ __global__ void latent_prepare_kernel(const TA* __restrict__ proj, long long ld,
 IX_API int ix_latent_prepare(const void* proj, long long ld, int q_off, int kv_off,
                              const int* positions, const float* freq, float mag,
                              const float* gain, float eps, const int* slots, void* cache,
-                             void* q_rot, int act_dtype, int T, int H, int dn, int dr,
-                             int rot_dims, int rank, cudaStream_t stream) {
+                             void* q_rot, void* q_plain, int act_dtype, int T, int H, int dn,
+                             int dr, int rot_dims, int rank, cudaStream_t stream) {
   if (T <= 0) return IX_OK;
   if (H <= 0 || dn < 0 || dr < 0 || rank <= 0 || rot_dims < 0 || rot_dims > dr || rot_dims % 2)
     return IX_ERR_SIZE;
@@ -94,7 +100,8 @@ IX_API int ix_latent_prepare(const void* proj, long long ld, int q_off, int kv_o
   IX_DISPATCH_DTYPE(act_dtype, TA,
                     ix_launch(latent_prepare_kernel<TA>, dim3(T), dim3(128), 0, stream,
                               (const TA*)proj, ld, q_off, kv_off, positions, freq, mag, gain, eps,
-                              slots, (TA*)cache, (TA*)q_rot, H, dn, dr, rot_dims, rank));
+                              slots, (TA*)cache, (TA*)q_rot, (TA*)q_plain, T, H, dn, dr, rot_dims,
+                              rank));
   return ix_launch_status();
 }
 

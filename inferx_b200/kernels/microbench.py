@@ -10,6 +10,7 @@
     python -m inferx_b200.kernels.microbench grouped --tokens 2048
     python -m inferx_b200.kernels.microbench latent_attn --tokens 2048 --rank 512 --rot-dim 64 [--form mma|general]
     python -m inferx_b200.kernels.microbench latent_attn --tokens 1 --batch 8 --context 4096
+    python -m inferx_b200.kernels.microbench rowwise --tokens 4096 --hidden 2048 --inter 5632
 
 Each case runs one kernel face at Qwen1.5-MoE-A2.7B sizes (or the sizes given),
 cycling through enough copies of its inputs that consecutive iterations do not
@@ -272,10 +273,49 @@ def latent_attn(args):
             "GBps": round(nbytes / us / 1e3, 1)}
 
 
+def rowwise(args):
+    """The row-wise kernels of the sublayer-norm decoders beside the like kernels of the
+    pre-norm ones, ``--tokens`` rows of ``--hidden`` (feed-forward ``--inter``): achieved
+    GB/s over the bytes the operation has to move."""
+    from . import ops
+    T, W, I = args.tokens, args.hidden, args.inter
+    dt = torch.bfloat16
+    n = max(2, min(8, _copies(T * W * 14)))
+    resid = [torch.randn(T, W, device="cuda") for _ in range(n)]
+    delta32 = [torch.randn(T, W, device="cuda") for _ in range(n)]
+    delta16 = [d.to(dt) for d in delta32]
+    gu = [torch.randn(T, 2 * I, device="cuda", dtype=dt) for _ in range(n)]
+    gain = torch.ones(W, device="cuda")
+    mix = torch.rand(W, device="cuda")
+    state = torch.zeros(2, W, device="cuda")
+    H, D = args.heads, args.head_dim
+    o = [torch.randn(H, T, D, device="cuda", dtype=dt) for _ in range(n)]
+    proj = [torch.randn(T, H * D, device="cuda", dtype=dt) for _ in range(n)]
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    step = types.SimpleNamespace(cu_q=i32([0, T]), seq_of_token=torch.zeros(T, dtype=torch.int32,
+                                                                            device="cuda"),
+                                 state_slot=i32([1]))
+    cases = {
+        "token_shift": (lambda i: ops.token_shift(resid[i], mix, state, step, dt), 6 * T * W),
+        "group_norm_add+cast": (lambda i: ops.group_norm_add(resid[i], delta32[i], gain, 4, 1e-5,
+                                                             dt), 14 * T * W),
+        "add_rmsnorm": (lambda i: ops.add_rmsnorm(resid[i], delta16[i], gain, 1e-5, dt),
+                        12 * T * W),
+        "glu_clamped": (lambda i: ops.glu_clamped(gu[i], 7.0, 1.702, 1.0), 6 * T * I),
+        "silu_mul": (lambda i: ops.silu_mul(gu[i]), 6 * T * I),
+        "gate_heads": (lambda i: ops.gate_heads(o[i], proj[i], 0), 6 * T * H * D),
+    }
+    out = {"case": "rowwise", "tokens": T, "hidden": W, "inter": I}
+    for name, (fn, nbytes) in cases.items():
+        us = _time(fn, n, args.iters)
+        out[name] = {"us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1)}
+    return out
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("case", choices=["attn_decode", "grouped", "dense", "attn_prefill", "router",
-                                     "qkv", "latent_attn"])
+                                     "qkv", "latent_attn", "rowwise"])
     ap.add_argument("--rank", type=int, default=512, help="latent_attn: entries of the latent")
     ap.add_argument("--rot-dim", type=int, default=64, help="latent_attn: rotated key entries")
     ap.add_argument("--iters", type=int, default=50)

@@ -807,11 +807,13 @@ SMALL_M_DENSE_ROWS = 16      # dense: up to this many rows stream the weights on
 def gemm_small_m(x: torch.Tensor, w: torch.Tensor, rows: Optional[torch.Tensor],
                  offsets: Optional[torch.Tensor], dual: bool, num_out_rows: int,
                  out_dtype: Optional[torch.dtype] = None, rows_per_pass: int = 8,
-                 active_groups: int = 0, offsets_settled: bool = False):
+                 active_groups: int = 0, offsets_settled: bool = False,
+                 glu_clamp: Optional[Tuple[float, float, float]] = None):
     """Weight-streaming product for few rows per weight matrix (bf16 inputs).
     ``offsets_settled``: the kernel that wrote ``offsets`` is at least two launches back
     in this stream (so the launch may read it, and start on its weights, before waiting
-    for its predecessor)."""
+    for its predecessor).  ``glu_clamp`` (dual only): (limit, slope, shift) of the clamped
+    gated unit instead of silu(gate) * up."""
     _chk("x", x, torch.bfloat16)
     _chk("w", w, torch.bfloat16)
     _chk("rows", rows, torch.int32, optional=True)
@@ -820,13 +822,17 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, rows: Optional[torch.Tensor],
     N = w_rows // 2 if dual else w_rows
     if x.shape[1] != K:
         raise KernelError(f"gemm_small_m: inner sizes differ ({x.shape[1]} vs {K})")
+    if glu_clamp is not None and (not dual or glu_clamp[0] <= 0):
+        raise KernelError("gemm_small_m: the clamped unit needs the dual form and a limit > 0")
+    limit, alpha, shift = glu_clamp if glu_clamp is not None else (0.0, 1.0, 0.0)
     out_dtype = out_dtype or x.dtype
     out = torch.empty((num_out_rows, N), dtype=out_dtype, device=x.device)
-    code = _lib().ix_gemm_small_m(
+    code = _lib().ix_gemm_small_m_act(
         _ptr(x), _ptr(rows), _ptr(offsets), _ptr(w), _ptr(out),
         F32 if out_dtype == torch.float32 else BF16, 1 if dual else 0,
         0 if offsets is not None else x.shape[0], N, K, E, rows_per_pass,
-        active_groups or min(E, num_out_rows), 1 if offsets_settled else 0, _stream())
+        active_groups or min(E, num_out_rows), 1 if offsets_settled else 0,
+        ctypes.c_float(limit), ctypes.c_float(alpha), ctypes.c_float(shift), _stream())
     _check(code, "gemm_small_m")
     _count()
     return out
@@ -1062,8 +1068,14 @@ def glu_clamped(gu: torch.Tensor, limit: float, alpha: float, up_shift: float):
 
 def gate_up_glu_clamped(x: torch.Tensor, w_gate_up: torch.Tensor, limit: float, alpha: float,
                         up_shift: float):
-    """Front half of a clamped-GLU feed-forward: the fused gate|up product, then the
-    activation."""
+    """Front half of a clamped-GLU feed-forward: the fused gate|up product and the
+    activation; one weight-streaming kernel for a few rows."""
+    _chk("x", x)
+    _chk("w_gate_up", w_gate_up, x.dtype)
+    M = x.shape[0]
+    if M <= SMALL_M_DENSE_ROWS and _streams_weights(x, w_gate_up) and limit > 0:
+        return gemm_small_m(x, w_gate_up.unsqueeze(0), None, None, True, M, rows_per_pass=M,
+                            glu_clamp=(limit, alpha, up_shift))
     return glu_clamped(linear(x, w_gate_up), limit, alpha, up_shift)
 
 
@@ -1079,8 +1091,28 @@ def batched_linear(x: torch.Tensor, w: torch.Tensor):
                           f"{tuple(w.shape)} {w.dtype}")
     if x.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
         raise KernelError("batched_linear: TF32 is switched on; 32-bit products must be exact")
+    B, M, K = x.shape
+    if (M <= SMALL_M_DENSE_ROWS and x.is_contiguous() and w.is_contiguous()
+            and _streams_weights(x, w)):
+        # a few rows per matrix: the weight-streaming kernel, one group per matrix
+        out = gemm_small_m(x.view(B * M, K), w, None, _even_offsets(B, M, x.device), False, B * M,
+                           rows_per_pass=8 if M <= 8 else 16, active_groups=B,
+                           offsets_settled=True)
+        return out.view(B, M, w.shape[1])
     LIBRARY_CALLS[0] += 1
     return torch.bmm(x, w.transpose(1, 2))
+
+
+_EVEN_OFFSETS: dict = {}
+
+
+def _even_offsets(groups: int, rows: int, device) -> torch.Tensor:
+    """[0, rows, 2 rows, ...]: group boundaries of ``groups`` matrices with ``rows`` rows
+    each, made once per shape (steps recorded into CUDA graphs keep pointing at it)."""
+    key = (groups, rows, str(device))
+    if key not in _EVEN_OFFSETS:
+        _EVEN_OFFSETS[key] = (torch.arange(groups + 1, dtype=torch.int32) * rows).to(device)
+    return _EVEN_OFFSETS[key]
 
 
 def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int, positions: torch.Tensor,
@@ -1092,7 +1124,8 @@ def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int, positions: torch
     (head h's query is ``dim`` plain then ``rot_dim`` rotated columns from ``q_off`` on;
     interleaved pairs, the first ``rot_dims`` entries turn), write the record
     [latent | rotated key] into ``cache`` ([pages, 1, page, rank + rot_dim]) at ``slots``.
-    Returns the rotated query parts [T, heads, rot_dim]."""
+    Returns the rotated query parts [T, heads, rot_dim] and the plain ones, heads
+    outermost, [heads, T, dim]."""
     _chk("proj", proj)
     _chk("positions", positions, torch.int32)
     _chk("freq", freq, torch.float32)
@@ -1107,13 +1140,14 @@ def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int, positions: torch
     if cache is not None and (cache.shape[1] != 1 or cache.shape[3] != rank + rot_dim):
         raise KernelError("latent_prepare: cache records must be [1, page, rank + rot_dim]")
     q_rot = torch.empty((T, heads, rot_dim), dtype=proj.dtype, device=proj.device)
+    q_plain = torch.empty((heads, T, dim), dtype=proj.dtype, device=proj.device)
     _check(_lib().ix_latent_prepare(
         _ptr(proj), ctypes.c_longlong(ld), q_off, kv_off, _ptr(positions), _ptr(freq),
         ctypes.c_float(mag), _ptr(gain), ctypes.c_float(eps), _ptr(slots), _ptr(cache),
-        _ptr(q_rot), _dtype_code(proj), T, heads, dim, rot_dim, rot_dims, rank, _stream()),
-        "latent_prepare")
+        _ptr(q_rot), _ptr(q_plain), _dtype_code(proj), T, heads, dim, rot_dim, rot_dims, rank,
+        _stream()), "latent_prepare")
     _count()
-    return q_rot
+    return q_rot, q_plain
 
 
 # Latent attention forms: "mma" (mma.sync tensor cores; bf16, latent sizes 64 / 128 / 256 /

@@ -91,12 +91,11 @@ class LatentAttentionMixer:
             freq, mag, rot_dims = self.position.pair_table()
         else:
             freq, mag, rot_dims = torch.empty(0, dtype=torch.float32, device=x.device), 1.0, 0
-        q_rot = ops.latent_prepare(
+        q_rot, q_plain = ops.latent_prepare(
             proj, 0, self.kv_off, step.positions, freq, mag, self.latent_gain, s.latent_eps,
             s.heads, s.dim, s.rot_dim, rot_dims, s.kv_rank,
             records if cache.writes else None, group.slots if cache.writes else None)
-        q_plain = proj[:, :self.q_width].view(T, s.heads, s.dim + s.rot_dim)[:, :, :s.dim]
-        q_lat = ops.batched_linear(q_plain.transpose(0, 1), self.uk_t)       # [heads, T, rank]
+        q_lat = ops.batched_linear(q_plain, self.uk_t)                       # [heads, T, rank]
         mixed = ops.latent_attention(q_lat, q_rot, records, group.block_table, step, s.window,
                                      s.scale)                                # [heads, T, rank]
         o = ops.batched_linear(mixed, self.uv)                               # [heads, T, vdim]

@@ -354,7 +354,8 @@ def latent_prepare(proj, q_off, kv_off, positions, freq, mag, gain, eps, heads, 
                          rot_dims)
         _scatter(cache, torch.cat([c, kr], dim=-1)[:, None, :], slots)
     q = x[:, q_off:q_off + heads * (dim + rot_dim)].reshape(T, heads, dim + rot_dim)
-    return _turn_pairs(q[..., dim:], positions, freq, mag, rot_dims).contiguous().to(proj.dtype)
+    q_rot = _turn_pairs(q[..., dim:], positions, freq, mag, rot_dims).contiguous().to(proj.dtype)
+    return q_rot, q[..., :dim].transpose(0, 1).contiguous().to(proj.dtype)
 
 
 def latent_attention(q_lat, q_rot, cache, block_table, step, window, scale):

@@ -140,19 +140,47 @@ def test_latent_prepare(dtype, H, dn, dr, rot_dims, rank):
     slots = torch.randperm(P * page, generator=g)[:T].to(torch.int32)
     cache = torch.zeros(P, 1, page, rank + dr, dtype=dtype)
     c_ref = cache.clone()
-    ref = host_ops.latent_prepare(proj, q_off, kv_off, step.positions, freq, 1.3, gain, 1e-5, H,
-                                  dn, dr, rot_dims, rank, c_ref, slots)
+    ref, ref_plain = host_ops.latent_prepare(proj, q_off, kv_off, step.positions, freq, 1.3, gain,
+                                             1e-5, H, dn, dr, rot_dims, rank, c_ref, slots)
     c = cache.cuda()
-    out = _ops().latent_prepare(proj.cuda(), q_off, kv_off, step.positions.cuda(), freq.cuda(),
+    out, plain_part = _ops().latent_prepare(proj.cuda(), q_off, kv_off, step.positions.cuda(), freq.cuda(),
                                 1.3, gain.cuda(), 1e-5, H, dn, dr, rot_dims, rank, c, slots.cuda())
     # angles reach 900 radians: fp32 cos/sin of an fp32 product on both sides
     tol = dict(rtol=2e-4, atol=2e-4) if dtype == torch.float32 else _tol(dtype)
     torch.testing.assert_close(out.cpu().float(), ref.float(), **tol)
+    assert torch.equal(plain_part.cpu(), ref_plain)
     torch.testing.assert_close(c.cpu().float(), c_ref.float(), **tol)
     # without a cache only the queries are produced
-    out2 = _ops().latent_prepare(proj.cuda(), q_off, kv_off, step.positions.cuda(), freq.cuda(),
-                                 1.3, gain.cuda(), 1e-5, H, dn, dr, rot_dims, rank, None, None)
+    out2, _ = _ops().latent_prepare(proj.cuda(), q_off, kv_off, step.positions.cuda(),
+                                    freq.cuda(), 1.3, gain.cuda(), 1e-5, H, dn, dr, rot_dims, rank,
+                                    None, None)
     assert torch.equal(out2, out)
+
+
+@pytest.mark.parametrize("M", [1, 8, 16, 40])
+def test_products_batched_over_heads(M):
+    """A few rows per head go through the weight-streaming kernel, more through the
+    library; both against the plain product."""
+    g = torch.Generator().manual_seed(M)
+    for dtype, B, N, K in ((torch.bfloat16, 16, 512, 128), (torch.bfloat16, 5, 40, 24),
+                           (torch.float32, 3, 20, 40)):
+        x = torch.randn(B, M, K, generator=g).to(dtype)
+        w = (torch.randn(B, N, K, generator=g) * 0.2).to(dtype)
+        ref = host_ops.batched_linear(x, w)
+        out = _ops().batched_linear(x.cuda(), w.cuda())
+        torch.testing.assert_close(out.cpu().float(), ref.float(), **_tol(dtype))
+
+
+@pytest.mark.parametrize("M", [1, 7, 16])
+def test_clamped_glu_fused_into_the_small_product(M):
+    g = torch.Generator().manual_seed(M)
+    I, K = 320, 256
+    w = (torch.randn(2 * I, K, generator=g) * 0.2).to(torch.bfloat16)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    ref = host_ops.glu_clamped(host_ops.linear(x.float(), w.float()), 1.1, 1.702, 1.0)
+    out = _ops().gate_up_glu_clamped(x.cuda(), w.cuda(), 1.1, 1.702, 1.0)
+    torch.testing.assert_close(out.cpu().float(), ref, rtol=2e-2, atol=2e-2)
+    assert float(out.float().max()) > 1.0
 
 
 def _attention_case(seed, H, rank, dr, page, q_lens, starts, dtype, spread=1.0):
