@@ -17,7 +17,8 @@ from inferx_b200.config.model_config import ConfigError
 from inferx_b200.config.registry import config_from_json
 from inferx_b200.engine.replay import ReplaySession
 
-CASES = [("ZA", zc.ZA, 0, [5, 9, 17, 40, 3, 70], 4), ("ZB", zc.ZB, 1, [1, 6, 13, 31, 45, 80], 8)]
+CASES = [("ZA", zc.ZA, 0, [5, 9, 17, 40, 3, 70], 4), ("ZB", zc.ZB, 1, [1, 6, 13, 31, 45, 80], 8),
+         ("ZD", zc.ZD, 3, [21, 1, 50, 2, 37], 4)]
 
 
 # -- configuration ---------------------------------------------------------------

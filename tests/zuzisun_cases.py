@@ -60,6 +60,19 @@ ZC = {
 }
 
 
+# nothing a multiple of 8, an odd vocabulary, one head, a window of one page and of two tokens
+ZD = {
+    "architecture": "Zuzisun", "vocab": 101, "width": 60, "embedding": {"scale": 0.7},
+    "norm": {"eps": 1e-5, "groups": 5},
+    "layers": [
+        latent_layer(3, 10, 6, 14, 22, 0.3, window=4, rot_dims=4, scaling=(3.0, 16, 4.0, 0.5), ff=50,
+                     limit=1.0),
+        latent_layer(1, 18, 2, 9, 13, 0.4, window=2, base=50.0, ff=26, limit=3.0),
+        latent_layer(7, 4, 10, 6, 30, 0.5, rot_dims=0),
+    ],
+}
+
+
 def sharpen(name, t):
     """N(0, 0.02) weights would give uniform attention, a dead gate, clamps that never
     act and a shift of nothing; make each of them matter."""
