@@ -25,6 +25,8 @@
 // Pair i < rot_dims / 2 of a rotated part is (2i, 2i+1), turned by pos * freq[i];
 // cos and sin are multiplied by `mag`; entries from rot_dims on pass unchanged.
 // ---------------------------------------------------------------------------
+#define LP_HEADS 4   // heads a block of the preparation handles
+
 template <typename TA>
 __global__ void latent_prepare_kernel(const TA* __restrict__ proj, long long ld, int q_off,
                                       int kv_off, const int* __restrict__ positions,
@@ -39,7 +41,9 @@ __global__ void latent_prepare_kernel(const TA* __restrict__ proj, long long ld,
   const TA* row = proj + (size_t)t * ld;
   const float pos = (float)positions[t];
   const int half = rot_dims >> 1;
-  if (cache != nullptr) {
+  // blockIdx.y: a group of LP_HEADS heads; the first group also makes the token's record
+  const int h_lo = blockIdx.y * LP_HEADS, h_n = min(LP_HEADS, H - h_lo);
+  if (cache != nullptr && blockIdx.y == 0) {
     const TA* kv = row + kv_off;
     float ss = 0.f;
     for (int i = threadIdx.x; i < rank; i += blockDim.x) {
@@ -65,13 +69,13 @@ __global__ void latent_prepare_kernel(const TA* __restrict__ proj, long long ld,
     }
   }
   // the plain query parts, heads outermost: [H, T, dn]
-  for (int idx = threadIdx.x; idx < H * dn; idx += blockDim.x) {
-    const int h = idx / dn, d = idx - h * dn;
+  for (int idx = threadIdx.x; idx < h_n * dn; idx += blockDim.x) {
+    const int h = h_lo + idx / dn, d = idx % dn;
     q_plain[((size_t)h * T + t) * dn + d] = row[q_off + (size_t)h * (dn + dr) + d];
   }
   const int pairs = (dr + 1) / 2;
-  for (int idx = threadIdx.x; idx < H * pairs; idx += blockDim.x) {
-    const int h = idx / pairs, p = idx - h * pairs;
+  for (int idx = threadIdx.x; idx < h_n * pairs; idx += blockDim.x) {
+    const int h = h_lo + idx / pairs, p = idx % pairs;
     const TA* q = row + q_off + (size_t)h * (dn + dr) + dn;
     const float u = to_f32(q[2 * p]);
     const float v = 2 * p + 1 < dr ? to_f32(q[2 * p + 1]) : 0.f;
@@ -98,7 +102,8 @@ IX_API int ix_latent_prepare(const void* proj, long long ld, int q_off, int kv_o
     return IX_ERR_SIZE;
   if (cache != nullptr && slots == nullptr) return IX_ERR_SIZE;
   IX_DISPATCH_DTYPE(act_dtype, TA,
-                    ix_launch(latent_prepare_kernel<TA>, dim3(T), dim3(128), 0, stream,
+                    ix_launch(latent_prepare_kernel<TA>, dim3(T, (H + LP_HEADS - 1) / LP_HEADS),
+                              dim3(128), 0, stream,
                               (const TA*)proj, ld, q_off, kv_off, positions, freq, mag, gain, eps,
                               slots, (TA*)cache, (TA*)q_rot, (TA*)q_plain, T, H, dn, dr, rot_dims,
                               rank));

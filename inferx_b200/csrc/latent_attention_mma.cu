@@ -89,6 +89,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ q_lat, long long ql_sh, lon
   constexpr int RPW = 16 / NSPLIT;         // rows whose softmax a warp owns
   constexpr int LPR = 32 / RPW;            // lanes per such row
   constexpr int CPL = 32 / LPR;            // keys per lane
+  constexpr bool PIPELINED = NSPLIT < 4;
   extern __shared__ __align__(16) unsigned char lm_smem[];
   IX_PDL_WAIT();
   const int Dk = RANK + dr;
@@ -210,15 +211,47 @@ latent_attention_mma_kernel(const bf16* __restrict__ q_lat, long long ql_sh, lon
       for (int n = 0; n < 4; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
       const bf16* qa = Qs + (rg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ld + (lane >> 4) * 8;
       const bf16* kb = Kb + ((lane & 7) + (lane >> 4) * 8) * ld + ((lane >> 3) & 1) * 8;
-      for (int ks = cg; ks < ksteps; ks += NSPLIT) {
-        unsigned a[4], b0, b1, b2, b3;
-        lm_ldsm4(a[0], a[1], a[2], a[3], qa + ks * 16);
-        lm_ldsm4(b0, b1, b2, b3, kb + ks * 16);
-        lm_mma(acc[0], a, b0, b1);
-        lm_mma(acc[1], a, b2, b3);
-        lm_ldsm4(b0, b1, b2, b3, kb + 16 * ld + ks * 16);
-        lm_mma(acc[2], a, b0, b1);
-        lm_mma(acc[3], a, b2, b3);
+      // PIPELINED (set where the kernel is declared): fragments of the next slice are
+      // fetched before the products of this one are issued.  With sixteen warps at the
+      // 128-register limit that measured slower (137 against 148 TFLOP/s), with eight or
+      // four warps faster (129 against 108).
+      if constexpr (PIPELINED) {
+        unsigned a[4], b[8];
+        if (cg < ksteps) {
+          lm_ldsm4(a[0], a[1], a[2], a[3], qa + cg * 16);
+          lm_ldsm4(b[0], b[1], b[2], b[3], kb + cg * 16);
+          lm_ldsm4(b[4], b[5], b[6], b[7], kb + 16 * ld + cg * 16);
+        }
+        for (int ks = cg; ks < ksteps; ks += NSPLIT) {
+          unsigned an[4], bn[8];
+          const int kn = ks + NSPLIT;
+          if (kn < ksteps) {
+            lm_ldsm4(an[0], an[1], an[2], an[3], qa + kn * 16);
+            lm_ldsm4(bn[0], bn[1], bn[2], bn[3], kb + kn * 16);
+            lm_ldsm4(bn[4], bn[5], bn[6], bn[7], kb + 16 * ld + kn * 16);
+          }
+          lm_mma(acc[0], a, b[0], b[1]);
+          lm_mma(acc[1], a, b[2], b[3]);
+          lm_mma(acc[2], a, b[4], b[5]);
+          lm_mma(acc[3], a, b[6], b[7]);
+          if (kn < ksteps) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = an[i];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) b[i] = bn[i];
+          }
+        }
+      } else {
+        for (int ks = cg; ks < ksteps; ks += NSPLIT) {
+          unsigned a[4], b0, b1, b2, b3;
+          lm_ldsm4(a[0], a[1], a[2], a[3], qa + ks * 16);
+          lm_ldsm4(b0, b1, b2, b3, kb + ks * 16);
+          lm_mma(acc[0], a, b0, b1);
+          lm_mma(acc[1], a, b2, b3);
+          lm_ldsm4(b0, b1, b2, b3, kb + 16 * ld + ks * 16);
+          lm_mma(acc[2], a, b0, b1);
+          lm_mma(acc[3], a, b2, b3);
+        }
       }
       float* d0 = Sp + (cg * LM_ROWS + rg * 16 + g) * LM_SLD + 2 * t4;
 #pragma unroll
@@ -285,16 +318,39 @@ latent_attention_mma_kernel(const bf16* __restrict__ q_lat, long long ql_sh, lon
       }
       const bf16* pa_src = Ps + (rg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LM_PLD + (lane >> 4) * 8;
       const bf16* vb = Kb + ((lane & 7) + ((lane >> 3) & 1) * 8) * ld + cg * CW + (lane >> 4) * 8;
+      if constexpr (PIPELINED) {
+        unsigned pa[2][4];
+        lm_ldsm4(pa[0][0], pa[0][1], pa[0][2], pa[0][3], pa_src);
+        lm_ldsm4(pa[1][0], pa[1][1], pa[1][2], pa[1][3], pa_src + 16);
+        // 2 x CW / 16 steps, each one 16 keys x 16 columns; the next step's latents are
+        // fetched before this step's products are issued
+        constexpr int STEPS = 2 * (CW / 16);
+        unsigned vb0, vb1, vb2, vb3;
+        lm_ldsm4t(vb0, vb1, vb2, vb3, vb);
 #pragma unroll
-      for (int ks2 = 0; ks2 < 2; ++ks2) {
-        unsigned pa[4];
-        lm_ldsm4(pa[0], pa[1], pa[2], pa[3], pa_src + ks2 * 16);
+        for (int st = 0; st < STEPS; ++st) {
+          const int ks2 = st / (CW / 16), np = st % (CW / 16);
+          unsigned n0 = 0, n1 = 0, n2 = 0, n3 = 0;
+          if (st + 1 < STEPS) {
+            const int ks2n = (st + 1) / (CW / 16), npn = (st + 1) % (CW / 16);
+            lm_ldsm4t(n0, n1, n2, n3, vb + ks2n * 16 * ld + npn * 16);
+          }
+          lm_mma(o[2 * np], pa[ks2], vb0, vb1);
+          lm_mma(o[2 * np + 1], pa[ks2], vb2, vb3);
+          vb0 = n0; vb1 = n1; vb2 = n2; vb3 = n3;
+        }
+      } else {
 #pragma unroll
-        for (int np = 0; np < CW / 16; ++np) {
-          unsigned b0, b1, b2, b3;
-          lm_ldsm4t(b0, b1, b2, b3, vb + ks2 * 16 * ld + np * 16);
-          lm_mma(o[2 * np], pa, b0, b1);
-          lm_mma(o[2 * np + 1], pa, b2, b3);
+        for (int ks2 = 0; ks2 < 2; ++ks2) {
+          unsigned pa[4];
+          lm_ldsm4(pa[0], pa[1], pa[2], pa[3], pa_src + ks2 * 16);
+#pragma unroll
+          for (int np = 0; np < CW / 16; ++np) {
+            unsigned b0, b1, b2, b3;
+            lm_ldsm4t(b0, b1, b2, b3, vb + ks2 * 16 * ld + np * 16);
+            lm_mma(o[2 * np], pa, b0, b1);
+            lm_mma(o[2 * np + 1], pa, b2, b3);
+          }
         }
       }
     }
@@ -334,27 +390,40 @@ latent_attention_mma_kernel(const bf16* __restrict__ q_lat, long long ql_sh, lon
   }
 }
 
-// Merge of the chunks' partial results, in chunk order: one block per (token, head).
+// Merge of the chunks' partial results, in chunk order: one block per (token, head).  The
+// chunks' weights exp2(m_i - m) are formed once, in shared memory.
 __global__ void latent_attention_merge_kernel(const float* __restrict__ part_o,
                                               const float* __restrict__ part_ml, int nsplit,
                                               bf16* __restrict__ out, long long o_sh,
                                               long long o_st, int H, int rank) {
+  extern __shared__ float merge_w[];     // [nsplit]
+  __shared__ float scratch[32];
   IX_PDL_WAIT();
   const int tok = blockIdx.x / H, h = blockIdx.x % H;
   const float* ml = part_ml + (size_t)blockIdx.x * nsplit * 2;
   float m = -INFINITY;
-  for (int i = 0; i < nsplit; ++i)
+  for (int i = threadIdx.x; i < nsplit; i += blockDim.x)
     if (ml[2 * i + 1] > 0.f) m = fmaxf(m, ml[2 * i]);
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = -INFINITY;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) m = fmaxf(m, scratch[w]);
+  for (int i = threadIdx.x; i < nsplit; i += blockDim.x)
+    merge_w[i] = ml[2 * i + 1] > 0.f ? exp2f(ml[2 * i] - m) : 0.f;
+  __syncthreads();
   float l = 0.f;
-  for (int i = 0; i < nsplit; ++i)
-    if (ml[2 * i + 1] > 0.f) l += ml[2 * i + 1] * exp2f(ml[2 * i] - m);
+  for (int i = 0; i < nsplit; ++i) l += merge_w[i] * ml[2 * i + 1];    // chunk order
   const float inv = l > 0.f ? 1.0f / l : 0.f;
   const float* po = part_o + (size_t)blockIdx.x * nsplit * rank;
   bf16* dst = out + (size_t)h * o_sh + (size_t)tok * o_st;
   for (int d = threadIdx.x; d < rank; d += blockDim.x) {
     float acc = 0.f;
-    for (int i = 0; i < nsplit; ++i)
-      if (ml[2 * i + 1] > 0.f) acc += po[(size_t)i * rank + d] * exp2f(ml[2 * i] - m);
+#pragma unroll 4
+    for (int i = 0; i < nsplit; ++i) {
+      const float w = merge_w[i];
+      if (w > 0.f) acc += po[(size_t)i * rank + d] * w;   // an empty chunk's output was never written
+    }
     dst[d] = __float2bfloat16_rn(acc * inv);
   }
 }
@@ -459,7 +528,8 @@ IX_API int ix_latent_attention_mma(const void* q_lat, long long ql_sh, long long
 #undef IX_LM
 #undef IX_LM1
   if (code != IX_OK || chunk_tiles <= 0) return code;
-  ix_launch(latent_attention_merge_kernel, dim3(T * H), dim3(128), 0, stream,
+  ix_launch(latent_attention_merge_kernel, dim3(T * H), dim3(rank >= 256 ? 256 : 128),
+            (size_t)nchunks * sizeof(float), stream,
             (const float*)part_o, (const float*)part_ml, nchunks, (bf16*)out, o_sh, o_st, H, rank);
   return ix_launch_status();
 }

@@ -1082,7 +1082,10 @@ def gate_up_glu_clamped(x: torch.Tensor, w_gate_up: torch.Tensor, limit: float, 
 def batched_linear(x: torch.Tensor, w: torch.Tensor):
     """out[b] = x[b] . w[b]^T for x [B, M, K] (any strides with unit inner stride) and
     w [B, N, K]: one library call batched over the leading dimension (per-head
-    products).  float32 operands are multiplied in true 32-bit."""
+    products).  float32 operands are multiplied in true 32-bit.  (For a few rows per
+    matrix the grouped weight-streaming kernel, one group per matrix, was measured too:
+    equal at 16 heads, slower at 8 and at 32 - a decode step of 0.85 against 0.74 ms at
+    width 4096 -, so the library keeps these products at every size.)"""
     if not (x.is_cuda and w.is_cuda):
         raise KernelError("batched_linear: tensors must be on a CUDA device")
     if x.dtype != w.dtype or x.dim() != 3 or w.dim() != 3 or x.shape[0] != w.shape[0] \
@@ -1091,28 +1094,8 @@ def batched_linear(x: torch.Tensor, w: torch.Tensor):
                           f"{tuple(w.shape)} {w.dtype}")
     if x.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
         raise KernelError("batched_linear: TF32 is switched on; 32-bit products must be exact")
-    B, M, K = x.shape
-    if (M <= SMALL_M_DENSE_ROWS and x.is_contiguous() and w.is_contiguous()
-            and _streams_weights(x, w)):
-        # a few rows per matrix: the weight-streaming kernel, one group per matrix
-        out = gemm_small_m(x.view(B * M, K), w, None, _even_offsets(B, M, x.device), False, B * M,
-                           rows_per_pass=8 if M <= 8 else 16, active_groups=B,
-                           offsets_settled=True)
-        return out.view(B, M, w.shape[1])
     LIBRARY_CALLS[0] += 1
     return torch.bmm(x, w.transpose(1, 2))
-
-
-_EVEN_OFFSETS: dict = {}
-
-
-def _even_offsets(groups: int, rows: int, device) -> torch.Tensor:
-    """[0, rows, 2 rows, ...]: group boundaries of ``groups`` matrices with ``rows`` rows
-    each, made once per shape (steps recorded into CUDA graphs keep pointing at it)."""
-    key = (groups, rows, str(device))
-    if key not in _EVEN_OFFSETS:
-        _EVEN_OFFSETS[key] = (torch.arange(groups + 1, dtype=torch.int32) * rows).to(device)
-    return _EVEN_OFFSETS[key]
 
 
 def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int, positions: torch.Tensor,
