@@ -17,6 +17,10 @@ live requests) over its time, against the measured copy bandwidth.
 ``--sizes 57b-a14b`` runs the same measurements at the Qwen2-57B-A14B layer sizes
 (context 32768, the wide point at batch 32 and the longest context that fits).
 
+``--designs`` is a separate report and leaves the default line alone: one JSON line per
+size (``--design-sizes 1k,2k,4k``) with the prompt and decode throughput of the Zuzisun
+design beside Qwen2-MoE with every layer dense at equal sizes.
+
 A decode step's working set (gigabytes of weights and cache) is far larger than the
 126 MB L2, so nothing stays resident between timed iterations.
 """
