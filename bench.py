@@ -769,8 +769,8 @@ def serving_check(args):
 # at equal width, depth, heads, feed-forward width, window and vocabulary.  Random weights.
 DESIGN_SIZES = {
     # name: width, heads, plain/rotated/value entries per head, latent, ff, window, twin kv heads
-    "1k": dict(width=1024, heads=8, dim=64, rot=32, vdim=64, rank=256, ff=2816, window=1024,
-               twin_head=64, twin_kv=8),
+    "1k": dict(width=1024, heads=8, dim=96, rot=32, vdim=128, rank=256, ff=2816, window=1024,
+               twin_head=128, twin_kv=8),
     "2k": dict(width=2048, heads=16, dim=128, rot=64, vdim=128, rank=512, ff=5632, window=4096,
                twin_head=128, twin_kv=16),
     "4k": dict(width=4096, heads=32, dim=128, rot=64, vdim=128, rank=512, ff=11008, window=4096,
@@ -784,10 +784,10 @@ def design_configs(z, layers):
     mixer = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"],
              "kv_rank": z["rank"], "scale": 1.0 / math.sqrt(z["dim"] + z["rot"]),
              "mask": {"size": z["window"]},
-             "rot": {"base": 1000000.0, "dims": z["rot"],
-                     "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+             "rot": {"base": 10000.0, "dims": z["rot"],
+                     "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
     new = {"architecture": "Zuzisun", "vocab": DESIGN_VOCAB, "width": z["width"],
-           "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5, "groups": 4},
+           "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6, "groups": 8},
            "layers": [{"type": "latent_attention", "mixer": mixer,
                        "mlp": {"kind": "dense", "ff": z["ff"], "limit": 7.0}}] * layers}
     twin = {"architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",

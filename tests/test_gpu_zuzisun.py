@@ -128,7 +128,7 @@ def test_output_gate(dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,dn,dr,rot_dims,rank", [(3, 24, 16, 16, 40), (2, 8, 24, 8, 24),
-                                                  (16, 64, 32, 32, 256), (1, 5, 6, 2, 7)])
+                                                  (16, 48, 32, 32, 256), (1, 5, 6, 2, 7)])
 def test_latent_prepare(dtype, H, dn, dr, rot_dims, rank):
     g = torch.Generator().manual_seed(rank)
     step = _step([4, 1, 3], [0, 900, 61])
@@ -205,7 +205,7 @@ def _attention_case(seed, H, rank, dr, page, q_lens, starts, dtype, spread=1.0):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,rank,dr,page,window", [(3, 40, 16, 4, 10), (5, 48, 8, 8, 0),
-                                                   (16, 256, 32, 16, 100), (8, 128, 32, 16, 136),
+                                                   (16, 256, 32, 16, 100), (8, 128, 48, 16, 90),
                                                    (1, 7, 6, 16, 3), (9, 160, 0, 32, 50),
                                                    (70, 64, 16, 8, 33), (5, 512, 64, 16, 0),
                                                    (64, 128, 0, 16, 77)])

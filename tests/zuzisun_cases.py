@@ -52,9 +52,9 @@ ZC = {
     "architecture": "Zuzisun", "vocab": 512, "width": 512, "embedding": {"scale": 1.5},
     "norm": {"eps": 1e-5, "groups": 8},
     "layers": [
-        latent_layer(16, 64, 32, 64, 256, 0.1, window=100, scaling=(4.0, 256, 32.0, 1.0), ff=1024,
+        latent_layer(16, 48, 32, 80, 256, 0.1, window=100, scaling=(6.0, 256, 16.0, 2.0), ff=1024,
                      limit=2.0),
-        latent_layer(16, 64, 32, 64, 256, 0.1, window=48, scaling=(4.0, 256, 32.0, 1.0), ff=1024,
+        latent_layer(16, 48, 32, 80, 256, 0.1, window=48, scaling=(6.0, 256, 16.0, 2.0), ff=1024,
                      limit=2.0),
     ],
 }
