@@ -33,6 +33,10 @@ def round_bf16(t):
     return t.to(torch.float32).to(torch.bfloat16).to(t.dtype)
 
 
+def round_f32(t):
+    return t.to(torch.float32).to(t.dtype)
+
+
 def same(t):
     return t
 
@@ -72,13 +76,19 @@ def rotary_frequencies(dims, base, scaling=None):
     return f, 0.1 * math.log(factor) + 1.0
 
 
-def rotate_interleaved(v, positions, freq, mag):
+def rotate_interleaved(v, positions, freq, mag, single=False):
     """v [n, ..., d]: the pairs (2i, 2i+1) for i < len(freq) are turned by
-    ``positions * freq[i]``; cos and sin carry the factor ``mag``; the rest passes."""
+    ``positions * freq[i]``; cos and sin carry the factor ``mag``; the rest passes.
+    ``single``: the angle, its cosine and its sine are formed in 32-bit, as an engine
+    forms them."""
     r = 2 * freq.numel()
     shape = [v.shape[0]] + [1] * (v.dim() - 2) + [freq.numel()]
-    a = (positions.to(F)[:, None] * freq[None, :]).reshape(shape)
-    c, s = torch.cos(a) * mag, torch.sin(a) * mag
+    if single:
+        a = (positions.to(torch.float32)[:, None] * freq.to(torch.float32)[None, :]).reshape(shape)
+        c, s = torch.cos(a).to(F) * mag, torch.sin(a).to(F) * mag
+    else:
+        a = (positions.to(F)[:, None] * freq[None, :]).reshape(shape)
+        c, s = torch.cos(a) * mag, torch.sin(a) * mag
     u, w = v[..., 0:r:2], v[..., 1:r:2]
     out = v.clone()
     out[..., 0:r:2] = u * c - w * s
@@ -95,7 +105,7 @@ def window_mask(n, size, offset=0):
     return (d >= 0) & ((d < size) if size > 0 else torch.ones_like(d, dtype=torch.bool))
 
 
-def latent_attention(h, m, w, prefix, eps, positions, rnd=same):
+def latent_attention(h, m, w, prefix, eps, positions, rnd=same, single=False):
     """The latent-attention mixer on its (already shifted) input ``h`` [n, width]."""
     H, dn, dr, dv, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     n = h.shape[0]
@@ -106,8 +116,8 @@ def latent_attention(h, m, w, prefix, eps, positions, rnd=same):
     c = rnd(c / torch.sqrt((c * c).mean(-1, keepdim=True) + eps) * W("dkv.norm"))
     rot = m["rot"]
     freq, mag = rotary_frequencies(rot["dims"], rot["base"], rot.get("scaling"))
-    k_rot = rnd(rotate_interleaved(down[:, None, rank:], positions, freq, mag))[:, 0]
-    q_rot = rnd(rotate_interleaved(q[..., dn:], positions, freq, mag))
+    k_rot = rnd(rotate_interleaved(down[:, None, rank:], positions, freq, mag, single))[:, 0]
+    q_rot = rnd(rotate_interleaved(q[..., dn:], positions, freq, mag, single))
     q_plain = q[..., :dn]
     k_plain = rnd(c @ W("uk").T).reshape(n, H, dn)
     v = rnd(c @ W("uv").T).reshape(n, H, dv)
@@ -132,9 +142,10 @@ def clamped_glu(h, f, w, prefix, rnd=same):
 
 
 # -- the model -----------------------------------------------------------------
-def forward(cfg, w, tokens, rnd=same, layers_out=None):
+def forward(cfg, w, tokens, rnd=same, layers_out=None, single_angles=False):
     """Logits [n, vocab] (float64) for one sequence from position 0.  ``rnd`` is
-    applied where an engine in bfloat16 stores an activation; ``layers_out``, a list,
+    applied where an engine stores an activation (``round_bf16``, ``round_f32``);
+    ``single_angles`` forms the rotation's angles in 32-bit; ``layers_out``, a list,
     receives the residual stream after every layer."""
     ids = torch.as_tensor(list(tokens), dtype=torch.long)
     n = ids.numel()
@@ -147,7 +158,8 @@ def forward(cfg, w, tokens, rnd=same, layers_out=None):
         if layer["type"] != "latent_attention":
             raise ValueError(f"unknown layer type {layer['type']!r}")
         h = rnd(token_shift(x, w[f"{p}.shift"].to(F)))
-        a = latent_attention(h, layer["mixer"], w, f"{p}.mix", eps, positions, rnd)
+        a = latent_attention(h, layer["mixer"], w, f"{p}.mix", eps, positions, rnd,
+                             single_angles)
         x = x + grouped_rms_norm(a, w[f"{p}.norm1"].to(F), groups, eps)
         if layer.get("mlp") is not None:
             if layer["mlp"]["kind"] != "dense":

@@ -300,7 +300,8 @@ def test_latent_attention_row_does_not_depend_on_its_batch():
 
 # -- the engine against the plain model ------------------------------------------------
 CASES = [("ZA", zc.ZA, 0, [5, 9, 17, 40, 3, 70], 4), ("ZB", zc.ZB, 1, [1, 6, 13, 31, 45, 80], 8),
-         ("ZC", zc.ZC, 2, [130, 2, 64, 33], 16), ("ZD", zc.ZD, 3, [21, 1, 50, 2, 37], 4)]
+         ("ZC", zc.ZC, 2, [130, 2, 64, 33], 16), ("ZD", zc.ZD, 3, [21, 1, 50, 2, 37], 4),
+         ("ZE", zc.ZE, 4, [150, 3, 77, 40], 16)]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

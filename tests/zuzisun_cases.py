@@ -73,6 +73,19 @@ ZD = {
 }
 
 
+# one layer for each latent size the tensor-core attention is built for, beside ZC's 256
+ZE = {
+    "architecture": "Zuzisun", "vocab": 300, "width": 192, "embedding": {"scale": 1.25},
+    "norm": {"eps": 1e-5, "groups": 2},
+    "layers": [
+        latent_layer(4, 32, 64, 32, 512, 0.12, window=70, scaling=(2.0, 64, 8.0, 1.0), ff=256,
+                     limit=1.5),
+        latent_layer(6, 40, 16, 24, 128, 0.2, base=1000.0, ff=128, limit=4.0),
+        latent_layer(2, 16, 48, 56, 64, 0.25, window=33, rot_dims=32),
+    ],
+}
+
+
 def sharpen(name, t):
     """N(0, 0.02) weights would give uniform attention, a dead gate, clamps that never
     act and a shift of nothing; make each of them matter."""
@@ -89,7 +102,18 @@ def sharpen(name, t):
     return t
 
 
-def make_model_dir(cfg, path, seed, dtype="float32", adjust=sharpen):
+def sharpen_mildly(name, t):
+    """For wide latents, where ``sharpen``'s factors turn attention into an argmax that
+    rounding flips: scores with a spread of a few units."""
+    if name.endswith((".mix.q", ".mix.uk")):
+        return t * 2.5
+    return sharpen(name, t)
+
+
+def make_model_dir(cfg, path, seed, dtype="float32", adjust=None):
+    if adjust is None:
+        wide = max(l["mixer"]["kv_rank"] for l in cfg["layers"]) >= 256
+        adjust = sharpen_mildly if wide else sharpen
     write_random_model(cfg, str(path), seed=seed, dtype=dtype, adjust=adjust)
     return str(path)
 
@@ -122,5 +146,19 @@ def bf16_bound(model_dir, requests, factor=3.0, floor=5e-3):
     return max(floor, factor * worst)
 
 
+def f32_bound(model_dir, requests, factor=3.0, floor=3e-5):
+    """The same for a 32-bit engine: activations stored in 32-bit and the rotation's angle,
+    cosine and sine formed in 32-bit (at position p and frequency f the angle alone is off
+    by up to p * f * 2^-24 radians, which a sharp score multiplies).  The floor stands for
+    what the plain model does not have: sums of hundreds of 32-bit products."""
+    cfg, w = plain.read_model_folder(model_dir)
+    worst = 0.0
+    for toks in requests.values():
+        a = plain.forward(cfg, w, toks)
+        b = plain.forward(cfg, w, toks, plain.round_f32, single_angles=True)
+        worst = max(worst, float((a - b).abs().max()) / float(a.abs().max()))
+    return max(floor, factor * worst)
+
+
 def bound_for(dtype, model_dir, requests):
-    return 3e-5 if dtype == "float32" else bf16_bound(model_dir, requests)
+    return f32_bound(model_dir, requests) if dtype == "float32" else bf16_bound(model_dir, requests)
