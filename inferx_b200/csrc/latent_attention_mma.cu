@@ -27,7 +27,6 @@
 // maximum, sum) go to scratch, and a second kernel merges them in chunk order.
 #include "common.cuh"
 
-#define LM_MAX_ROWS 64
 #define LM_KT 32
 #define LM_SLD 40   // floats per score row: 32 + 8, so that rows g and g + 1..3 hit other banks
 
@@ -42,12 +41,6 @@ __device__ __forceinline__ void lm_ldsm4(unsigned& r0, unsigned& r1, unsigned& r
   const unsigned a = (unsigned)__cvta_generic_to_shared(p);
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-               : "r"(a));
-}
-__device__ __forceinline__ void lm_ldsm2(unsigned& r0, unsigned& r1, const void* p) {
-  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];"
-               : "=r"(r0), "=r"(r1)
                : "r"(a));
 }
 __device__ __forceinline__ void lm_ldsm4t(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3,
