@@ -153,3 +153,22 @@ def test_greedy_generation_through_the_engine(tmp_path):
         for _ in range(6):
             seq.append(int(plain.forward(c, w, seq)[-1].argmax()))
         assert c_out.output_tokens == seq[len(p):]
+
+
+def test_preemption_rebuilds_shift_state_and_cache(tmp_path):
+    """A pool too small for all three requests: the preempted ones give back pages and
+    slot, start again from position 0 in a zeroed slot, and generate the same tokens."""
+    from inferx_b200 import Engine, EngineConfig, Request, SamplingParams
+    d = zc.make_model_dir(zc.ZB, tmp_path / "m", 0)
+    reqs = zc.make_requests(zc.ZB, [5, 9, 17], 0)
+
+    def run(pages):
+        eng = Engine.create(EngineConfig(model=d, dtype="float32", device="cpu", block_size=4,
+                                         max_num_seqs=3, num_gpu_blocks_override=pages,
+                                         max_model_len=64), ops=host_ops)
+        outs = eng.generate([Request(t, SamplingParams(max_tokens=8, ignore_eos=True))
+                             for t in reqs.values()])
+        return [c.output_tokens for c in outs], eng.stats()["preemptions"]
+    roomy, p0 = run(64)
+    tight, p1 = run(6)
+    assert p0 == 0 and p1 >= 1 and roomy == tight
