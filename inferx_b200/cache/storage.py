@@ -56,11 +56,13 @@ class CacheStorage:
             n += sum(t.numel() * t.element_size() for t in per.values())
         return n
 
-    def layer_caches(self, schedule) -> List[LayerCache]:
-        """One ``LayerCache`` per schedule entry."""
+    def layer_caches(self, schedule, unit_of=None) -> List[LayerCache]:
+        """One ``LayerCache`` per schedule entry.  ``unit_of(entry)`` gives the index of the
+        entry's cache among the needs this storage was built from (the layer it names,
+        when absent)."""
         out = []
         for e in schedule:
-            src = e.cache_layer
+            src = unit_of(e) if unit_of is not None else e.cache_layer
             out.append(LayerCache(
                 group=self.group_of_layer.get(src, -1), pages=self.paged.get(src, {}),
                 writes=e.writes_cache, state=self.state.get(src, {})))

@@ -60,6 +60,10 @@ def _register_builtin():
     from .zuzisun_config import ZuzisunConfig
     register_architecture(ZuzisunConfig.ARCHITECTURE, ZuzisunConfig.from_json,
                           zuzisun.build_spec, replace=True)
+    from ..models import tinapel
+    from .tinapel_config import TinapelConfig
+    register_architecture(TinapelConfig.ARCHITECTURE, TinapelConfig.from_json,
+                          tinapel.build_spec, replace=True)
 
 
 _register_builtin()

@@ -158,7 +158,8 @@ class Executor:
         self.storage = storage
         self.device = storage.device
         self.vocab = model.spec.vocab_size
-        self.caches = storage.layer_caches(model.spec.schedule)
+        self.caches = storage.layer_caches(model.spec.schedule,
+                                           getattr(model, "cache_unit", None))
         self.steps_run = 0
         self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
         self._graphs = GraphCache()

@@ -102,3 +102,59 @@ class AttentionMixer:
 
 
 register_part("mixer", "attention", AttentionMixer)
+
+
+class TiedKvAttentionMixer:
+    """Grouped-query attention whose values are its keys as projected: one projection
+    gives q and k, the raw k rows are stored as the values and the RMS-normed ones as the
+    keys (both in pages of the same shape, so every paged attention kernel serves), the
+    normed queries take the position's temperature, and the scores may be squashed by
+    tanh.  Norms, temperature and the squashing are fp32."""
+
+    def __init__(self, spec, ctx, prefix: str):
+        self.spec, self.ctx, self.prefix = spec, ctx, prefix
+        self.qk_w = self.o_w = self.q_gain = self.k_gain = None
+
+    def check_limits(self):
+        check = getattr(self.ctx.ops, "check_attention_limits", None)
+        if check is not None:
+            s = self.spec
+            check(s.heads, s.kv_heads, s.head_dim, self.ctx.dtype, self.prefix, allow_odd=True)
+
+    def _name(self, key):
+        return f"{self.prefix}.{dict(self.spec.names)[key]}"
+
+    def tensors(self):
+        s = self.spec
+        return [
+            TensorDecl(self._name("q"), (s.heads * s.head_dim, s.hidden)),
+            TensorDecl(self._name("k"), (s.kv_heads * s.head_dim, s.hidden)),
+            TensorDecl(self._name("q_norm"), (s.head_dim,), keep="float32", init="gain"),
+            TensorDecl(self._name("k_norm"), (s.head_dim,), keep="float32", init="gain"),
+            TensorDecl(self._name("o"), (s.hidden, s.heads * s.head_dim)),
+        ]
+
+    def bind(self, w):
+        self.qk_w = torch.cat([w[self._name("q")], w[self._name("k")]], dim=0).contiguous()
+        self.q_gain, self.k_gain = w[self._name("q_norm")], w[self._name("k_norm")]
+        self.o_w = w[self._name("o")]
+
+    def cache_needs(self):
+        return [PagedKvNeed(self.spec.kv_heads, self.spec.head_dim, self.spec.window)]
+
+    def forward(self, x, step, cache):
+        s, ops = self.spec, self.ctx.ops
+        group = step.groups[cache.group]
+        qk = ops.linear(x, self.qk_w)
+        q = ops.qk_norm_append(
+            qk, self.q_gain, self.k_gain, step.positions, s.heads, s.kv_heads, s.head_dim,
+            s.norm_eps, s.temp_coef, s.temp_every,
+            cache.k if cache.writes else None, cache.v if cache.writes else None,
+            group.slots if cache.writes else None)
+        attn = ops.paged_attention(q, cache.k, cache.v, group.block_table, step, s.window,
+                                   s.scale, softcap=s.softcap)
+        return ops.linear(attn.view(step.num_tokens, s.heads * s.head_dim), self.o_w,
+                          out_dtype=torch.float32)
+
+
+register_part("mixer", "attention_tied_kv", TiedKvAttentionMixer)

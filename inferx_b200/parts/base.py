@@ -14,6 +14,8 @@ Interfaces (duck-typed; a part defined outside this package works the same):
 * mixer: ``cache_needs() -> [PagedKvNeed | StateNeed]``,
   ``forward(x, step: StepContext, cache: LayerCache) -> [T, hidden]``.
 * feed-forward: ``forward(x, step) -> [T, hidden]``.
+* position encoding added to the embedding: ``embed(table, token_ids, positions, scale)
+  -> fp32 [T, hidden]``.
 * block (the arrangement of the parts of one layer): ``__init__(spec, ctx, prefix)``,
   ``parts() -> [part]``, ``cache_needs()``, ``forward(resid, pending, step, cache) ->
   pending`` on the fp32 residual stream (``pending`` is a contribution the next norm
@@ -116,6 +118,27 @@ class StepContext:
     # the two parts of a mixed batch to different kernels without gathering.
     num_decode_seqs: int = 0
     cu_q_prompt: Optional[torch.Tensor] = None   # [S - num_decode_seqs + 1] int32
+
+
+@dataclass
+class PendingSum:
+    """Contributions to the residual stream that have not been added yet: tensors
+    [T, width] (fp32 or the run's element type) and at most one fp32 vector [width]
+    added to every row.  A norm that knows this class adds them in the pass in which it
+    normalises; anything else calls ``materialize`` and adds the one tensor it gets."""
+    terms: List[Any] = field(default_factory=list)
+    vector: Optional[torch.Tensor] = None
+    dtype: Optional[torch.dtype] = None       # what ``materialize`` returns
+
+    def materialize(self) -> torch.Tensor:
+        total = None
+        for t in self.terms:
+            if hasattr(t, "materialize"):
+                t = t.materialize()
+            total = t.to(torch.float32) if total is None else total + t.to(torch.float32)
+        if self.vector is not None:
+            total = self.vector.to(torch.float32) if total is None else total + self.vector
+        return total.to(self.dtype or torch.float32)
 
 
 @dataclass

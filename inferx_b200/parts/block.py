@@ -18,7 +18,7 @@ import torch
 
 from ..weights import loader as wl
 from ..weights.loader import TensorDecl
-from .base import BuildContext, LayerCache, StepContext
+from .base import BuildContext, LayerCache, PendingSum, StepContext
 from .registry import build_part, register_part
 
 
@@ -96,6 +96,48 @@ class SublayerNormBlock:
         return None
 
 
+class ParallelBlock:
+    """``x += mixer(input_norm(x)) + ffn(post_norm(x))``: both sublayers read the same x,
+    each through a norm of its own, and their outputs are added to the stream together.
+    The sum is left pending, so the next norm adds it in the pass in which it normalises;
+    two RMS norms with the same eps are computed in one pass.  A layer may have no
+    feed-forward."""
+
+    def __init__(self, spec, ctx: BuildContext, prefix: str):
+        p = prefix
+        self.spec, self.ctx = spec, ctx
+        self.input_norm = build_part("norm", spec.input_norm, ctx, f"{p}.{spec.input_norm_name}")
+        self.mixer = build_part("mixer", spec.mixer, ctx, f"{p}.{spec.mixer_name}")
+        self.ffn = build_part("feed_forward", spec.ffn, ctx, f"{p}.{spec.ffn_name}")
+        self.post_norm = (build_part("norm", spec.post_norm, ctx, f"{p}.{spec.post_norm_name}")
+                          if self.ffn is not None else None)
+
+    def parts(self):
+        return [x for x in (self.input_norm, self.mixer, self.post_norm, self.ffn)
+                if x is not None]
+
+    def cache_needs(self):
+        return list(self.mixer.cache_needs())
+
+    def forward(self, resid, pending, step: StepContext, cache: LayerCache):
+        a_norm, f_norm = self.input_norm, self.post_norm
+        if f_norm is None:
+            if hasattr(pending, "materialize") and not getattr(a_norm, "accepts_pending", False):
+                pending = pending.materialize()
+            return self.mixer.forward(a_norm.forward(resid, pending), step, cache)
+        if hasattr(a_norm, "forward_pair") and hasattr(f_norm, "gain") and \
+                a_norm.spec.eps == f_norm.spec.eps:
+            na, nf = a_norm.forward_pair(resid, pending, f_norm)
+        else:
+            if hasattr(pending, "materialize") and not getattr(a_norm, "accepts_pending", False):
+                pending = pending.materialize()
+            na = a_norm.forward(resid, pending)
+            nf = f_norm.forward(resid, None)
+        a = self.mixer.forward(na, step, cache)
+        f = self.ffn.forward(nf, step)
+        return PendingSum(terms=[a, f], dtype=self.ctx.dtype)
+
+
 class DecoderModel:
     """Embedding, scheduled blocks, final norm and head, from a ``ModelSpec``."""
 
@@ -104,11 +146,25 @@ class DecoderModel:
         self.ctx = ctx
         self.blocks = [build_part("block", ls, ctx, ls.prefix) for ls in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, ctx, spec.final_norm_name)
+        self.embed_position = build_part("position", getattr(spec, "embed_position", None), ctx,
+                                         spec.embed_name)
         self.embed = None
         self.head = None
+        self.stream_tables = {}      # checkpoint name -> fp32 [rows, hidden]
         for e in spec.schedule:
             if not (0 <= e.layer < len(self.blocks)) or not (0 <= e.cache_layer < len(self.blocks)):
                 raise ValueError(f"schedule entry {e} names a layer that does not exist")
+            b = getattr(e, "before", None)
+            if b is not None and b.table is not None and not (0 <= b.row < b.rows):
+                raise ValueError(f"schedule entry {e} adds row {b.row} of {b.rows}")
+        # A cache unit is one layer's cache and state; a layer whose runs keep caches of
+        # their own has one unit per copy.  Units 0..L-1 are the layers' first copies.
+        extra = sorted({(e.cache_layer, e.cache_copy) for e in spec.schedule
+                        if getattr(e, "cache_copy", 0)})
+        self.cache_units = [(i, 0) for i in range(len(self.blocks))] + extra
+        self._unit_index = {u: i for i, u in enumerate(self.cache_units)}
+        self._keeps_embedding = any(getattr(e, "before", None) is not None and e.before.embedding
+                                    for e in spec.schedule)
         if ctx.ops is not None:
             # sizes beyond what the kernels take are refused now, not at the first launch
             for b in self.blocks:
@@ -122,6 +178,14 @@ class DecoderModel:
         decls = [TensorDecl(s.embed_name, (s.vocab_size, s.hidden))]
         if not s.tied_head:
             decls.append(TensorDecl(s.head_name, (s.vocab_size, s.hidden)))
+        tables = {}
+        for e in s.schedule:
+            b = getattr(e, "before", None)
+            if b is not None and b.table is not None:
+                if tables.setdefault(b.table, b.rows) != b.rows:
+                    raise ValueError(f"table {b.table!r} is given two sizes in the schedule")
+        decls += [TensorDecl(name, (rows, s.hidden), keep="float32", init="bias")
+                  for name, rows in tables.items()]
         return decls
 
     def tensors(self) -> List[TensorDecl]:
@@ -143,6 +207,8 @@ class DecoderModel:
         own = fetch(self._own_tensors())
         self.embed = own[self.spec.embed_name]
         self.head = self.embed if self.spec.tied_head else own[self.spec.head_name]
+        self.stream_tables = {n: t for n, t in own.items()
+                              if n not in (self.spec.embed_name, self.spec.head_name)}
         for b in self.blocks:
             for part in b.parts():
                 part.bind(fetch(part.tensors()))
@@ -150,8 +216,26 @@ class DecoderModel:
 
     # -- cache needs -------------------------------------------------------
     def cache_needs(self) -> List[list]:
-        """Per layer, what its mixer wants kept between steps."""
-        return [list(b.cache_needs()) for b in self.blocks]
+        """Per cache unit (a layer, or one of several copies of a layer's cache), what the
+        layer's mixer wants kept between steps."""
+        return [list(self.blocks[layer].cache_needs()) for layer, _ in self.cache_units]
+
+    def cache_unit(self, entry) -> int:
+        """The cache unit a schedule entry reads and writes."""
+        return self._unit_index[(entry.cache_layer, getattr(entry, "cache_copy", 0))]
+
+    def _add_before(self, pending, before, embedded):
+        """What a run's ``before`` names joins what is still to be added to the stream."""
+        terms = []
+        if pending is not None:
+            terms = list(pending.terms) if hasattr(pending, "terms") else [pending]
+        vector = getattr(pending, "vector", None)
+        if before.embedding:
+            terms.append(embedded)
+        if before.table is not None:
+            row = self.stream_tables[before.table][before.row]
+            vector = row if vector is None else vector + row
+        return PendingSum(terms=terms, vector=vector, dtype=self.ctx.dtype)
 
     # -- step --------------------------------------------------------------
     def forward(self, step: StepContext, caches: List[LayerCache],
@@ -161,12 +245,18 @@ class DecoderModel:
         ops = self.ctx.ops
         if hasattr(ops, "set_dependent_launch"):
             ops.set_dependent_launch(step.num_tokens <= ops.DEPENDENT_LAUNCH_MAX_TOKENS)
-        if self.spec.embed_scale != 1.0:
+        if self.embed_position is not None:
+            resid = self.embed_position.embed(self.embed, step.token_ids, step.positions,
+                                              self.spec.embed_scale)
+        elif self.spec.embed_scale != 1.0:
             resid = ops.embed(self.embed, step.token_ids, scale=self.spec.embed_scale)
         else:
             resid = ops.embed(self.embed, step.token_ids)
+        embedded = resid.clone() if self._keeps_embedding else None
         pending = None
         for entry, cache in zip(self.spec.schedule, caches):
+            if getattr(entry, "before", None) is not None:
+                pending = self._add_before(pending, entry.before, embedded)
             pending = self.blocks[entry.layer].forward(resid, pending, step, cache)
         if logit_rows is None or logit_rows.numel() == 0:
             return None
@@ -180,3 +270,4 @@ class DecoderModel:
 Block = PreNormBlock
 register_part("block", "pre_norm", PreNormBlock)
 register_part("block", "sublayer_norm", SublayerNormBlock)
+register_part("block", "parallel", ParallelBlock)

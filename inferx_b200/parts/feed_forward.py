@@ -25,19 +25,24 @@ class SwiGluFeedForward:
         self.spec, self.ctx, self.prefix = spec, ctx, prefix
         self.gate_up_w = self.down_w = None
 
+    def _names(self):
+        return getattr(self.spec, "names", ("gate_proj.weight", "up_proj.weight",
+                                            "down_proj.weight"))
+
     def tensors(self):
         s, p = self.spec, self.prefix
+        g, u, d = self._names()
         return [
-            TensorDecl(f"{p}.gate_proj.weight", (s.intermediate, s.hidden)),
-            TensorDecl(f"{p}.up_proj.weight", (s.intermediate, s.hidden)),
-            TensorDecl(f"{p}.down_proj.weight", (s.hidden, s.intermediate)),
+            TensorDecl(f"{p}.{g}", (s.intermediate, s.hidden)),
+            TensorDecl(f"{p}.{u}", (s.intermediate, s.hidden)),
+            TensorDecl(f"{p}.{d}", (s.hidden, s.intermediate)),
         ]
 
     def bind(self, w):
         p = self.prefix
-        self.gate_up_w = torch.cat([w[f"{p}.gate_proj.weight"], w[f"{p}.up_proj.weight"]],
-                                   dim=0).contiguous()
-        self.down_w = w[f"{p}.down_proj.weight"]
+        g, u, d = self._names()
+        self.gate_up_w = torch.cat([w[f"{p}.{g}"], w[f"{p}.{u}"]], dim=0).contiguous()
+        self.down_w = w[f"{p}.{d}"]
 
     def forward(self, x, step=None):
         ops = self.ctx.ops
@@ -100,14 +105,24 @@ class MoeFeedForward:
         if self.shared is not None and hasattr(self.shared, "check_limits"):
             self.shared.check_limits()
 
+    def _router_name(self):
+        return f"{self.prefix}.{getattr(self.spec, 'router_name', 'gate.weight')}"
+
+    def _expert_names(self, e: int):
+        names = getattr(self.spec, "expert_names", (
+            "experts.{e}.gate_proj.weight", "experts.{e}.up_proj.weight",
+            "experts.{e}.down_proj.weight"))
+        return tuple(f"{self.prefix}.{n.format(e=e)}" for n in names)
+
     def tensors(self):
         s, p = self.spec, self.prefix
-        decls = [TensorDecl(f"{p}.gate.weight", (s.num_experts, s.hidden), keep="float32")]
+        decls = [TensorDecl(self._router_name(), (s.num_experts, s.hidden), keep="float32")]
         for e in range(s.num_experts):
+            g, u, d = self._expert_names(e)
             decls += [
-                TensorDecl(f"{p}.experts.{e}.gate_proj.weight", (s.expert_intermediate, s.hidden)),
-                TensorDecl(f"{p}.experts.{e}.up_proj.weight", (s.expert_intermediate, s.hidden)),
-                TensorDecl(f"{p}.experts.{e}.down_proj.weight", (s.hidden, s.expert_intermediate)),
+                TensorDecl(g, (s.expert_intermediate, s.hidden)),
+                TensorDecl(u, (s.expert_intermediate, s.hidden)),
+                TensorDecl(d, (s.hidden, s.expert_intermediate)),
             ]
         if self.shared is not None:
             decls += self.shared.tensors()
@@ -118,15 +133,16 @@ class MoeFeedForward:
 
     def bind(self, w):
         s, p = self.spec, self.prefix
-        self.router_w = w[f"{p}.gate.weight"]
+        self.router_w = w[self._router_name()]
         gu = torch.empty((s.num_experts, 2 * s.expert_intermediate, s.hidden),
                          dtype=self.ctx.dtype, device=self.ctx.device)
         dn = torch.empty((s.num_experts, s.hidden, s.expert_intermediate),
                          dtype=self.ctx.dtype, device=self.ctx.device)
         for e in range(s.num_experts):
-            gu[e, :s.expert_intermediate] = w[f"{p}.experts.{e}.gate_proj.weight"]
-            gu[e, s.expert_intermediate:] = w[f"{p}.experts.{e}.up_proj.weight"]
-            dn[e] = w[f"{p}.experts.{e}.down_proj.weight"]
+            g, u, d = self._expert_names(e)
+            gu[e, :s.expert_intermediate] = w[g]
+            gu[e, s.expert_intermediate:] = w[u]
+            dn[e] = w[d]
         self.expert_gate_up, self.expert_down = gu, dn
         if self.shared is not None:
             self.shared.bind({d.name: w[d.name] for d in self.shared.tensors()})

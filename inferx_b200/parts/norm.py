@@ -2,7 +2,9 @@
 
 ``out = x * (1 / sqrt(mean(x^2) + eps)) * gain`` with the sum in fp32, no mean
 subtraction, no bias, the gain used as stored (not 1 + gain): the reference's
-RmsNormKernel (src/backends/cuda/ops/layers.cu:50-76).  The residual add that the
+RmsNormKernel (src/backends/cuda/ops/layers.cu:50-76).  A spec with ``gain_offset`` 1
+describes weights stored around zero; the offset is added once, in fp32, when the
+weights are bound.  The residual add that the
 reference does in a kernel of its own (layers.cu:542-548) happens in the same
 pass, on an fp32 residual stream.
 """
@@ -20,18 +22,34 @@ class RmsNorm:
     def __init__(self, spec, ctx, prefix: str):
         self.spec = spec
         self.ctx = ctx
-        self.name = f"{prefix}.weight"
+        self.name = f"{prefix}{getattr(spec, 'suffix', '.weight')}"
+        self.offset = float(getattr(spec, "gain_offset", 0.0))
         self.gain = None
 
     def tensors(self):
-        return [TensorDecl(self.name, (self.spec.size,), keep="float32", init="gain")]
+        # a weight stored around zero (the gain is offset + w) is drawn like a bias
+        return [TensorDecl(self.name, (self.spec.size,), keep="float32",
+                           init="bias" if self.offset else "gain")]
 
     def bind(self, weights):
         self.gain = weights[self.name]
+        if self.offset:
+            self.gain = (self.gain + self.offset).contiguous()    # fp32, once
 
     def forward(self, resid, delta, rows=None):
+        if hasattr(delta, "terms"):      # several contributions and a vector, one pass
+            return self.ctx.ops.add_rmsnorm_sum(resid, delta.terms, delta.vector, (self.gain,),
+                                                self.spec.eps, self.ctx.dtype, rows=rows)[0]
         return self.ctx.ops.add_rmsnorm(resid, delta, self.gain, self.spec.eps, self.ctx.dtype,
                                         rows=rows)
+
+    def forward_pair(self, resid, delta, other: "RmsNorm"):
+        """This norm's and ``other``'s view of the same rows (``resid`` after ``delta`` was
+        added), from one pass over the stream."""
+        terms = delta.terms if hasattr(delta, "terms") else ([] if delta is None else [delta])
+        vector = getattr(delta, "vector", None)
+        return self.ctx.ops.add_rmsnorm_sum(resid, terms, vector, (self.gain, other.gain),
+                                            self.spec.eps, self.ctx.dtype)
 
 
 register_part("norm", "rmsnorm", RmsNorm)

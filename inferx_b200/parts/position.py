@@ -78,3 +78,31 @@ class InterleavedRotary:
 
 
 register_part("position", "rope_interleaved", InterleavedRotary)
+
+
+class SinusoidAdded:
+    """A position vector added to the embedding: entry 2i of position p is
+    sin(p * base^(-2i/size)), entry 2i+1 the cosine of the same angle.  The frequencies
+    are computed once in float64 and rounded to fp32; the kernel forms the angle, its
+    sine and its cosine in fp32 with the accurate functions, in the pass that gathers and
+    scales the embedding rows."""
+
+    def __init__(self, spec, ctx, prefix: str):
+        self.spec, self.ctx = spec, ctx
+        pairs = (spec.size + 1) // 2
+        i = torch.arange(pairs, dtype=torch.float64)
+        freq = torch.pow(torch.tensor(float(spec.base), dtype=torch.float64),
+                         -2.0 * i / float(spec.size))
+        self.freq = freq.to(torch.float32).to(ctx.device)
+
+    def tensors(self):
+        return []
+
+    def bind(self, weights):
+        pass
+
+    def embed(self, table, token_ids, positions, scale: float):
+        return self.ctx.ops.embed_sinusoid(table, token_ids, positions, self.freq, scale)
+
+
+register_part("position", "sinusoid_added", SinusoidAdded)

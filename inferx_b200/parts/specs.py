@@ -20,9 +20,22 @@ from typing import Any, Optional
 
 @dataclass(frozen=True)
 class RmsNormSpec:
+    """x / sqrt(mean(x^2) + eps) * (gain_offset + w).  ``gain_offset`` is 1 for weights
+    stored around zero; ``suffix`` is what the tensor's name adds to the part's prefix."""
     size: int
     eps: float
+    gain_offset: float = 0.0
+    suffix: str = ".weight"
     kind: str = "rmsnorm"
+
+
+@dataclass(frozen=True)
+class SinusoidSpec:
+    """A position vector added to the embedding: entry 2i is sin(p * base^(-2i/size)),
+    entry 2i+1 the cosine of the same angle."""
+    size: int
+    base: float = 10000.0
+    kind: str = "sinusoid_added"
 
 
 @dataclass(frozen=True)
@@ -122,9 +135,67 @@ class AttentionSpec:
 
 
 @dataclass(frozen=True)
+class TiedKvAttentionSpec:
+    """Grouped-query softmax attention whose values are its keys as projected.  Queries
+    and keys are RMS-normed per head (gains ``q.norm`` / ``k.norm`` shared by the heads)
+    after the values were taken; no rotation.  The query at position p is multiplied by
+    1 + temp_coef * ln(floor((p + 1) / temp_every) + 1) (``temp_every`` 0: not at all);
+    scores are (q . k) * scale and, with ``softcap`` > 0, softcap * tanh(score / softcap)."""
+    hidden: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+    scale: float
+    norm_eps: float
+    softcap: float = 0.0
+    temp_coef: float = 0.0
+    temp_every: int = 0
+    window: int = 0
+    names: tuple = (("q", "q"), ("k", "k"), ("q_norm", "q.norm"), ("k_norm", "k.norm"),
+                    ("o", "o"))
+    kind: str = "attention_tied_kv"
+
+
+@dataclass(frozen=True)
+class GatedLinearAttentionSpec:
+    """Linear attention with a decay per key channel and a state [heads, dim, vdim] per
+    request: S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t with q scaled by
+    ``q_scale``; a_t = sigmoid(z_t)^(1 / tau), z_t = W_a2 (W_a1 h) + b, a low-rank product
+    whose inner size ``decay_rank`` is the checkpoint's when 0.  Each head's output is
+    RMS-normed over vdim (gain shared by the heads), multiplied by silu(W_g h), projected."""
+    hidden: int
+    heads: int
+    dim: int
+    vdim: int
+    tau: float
+    q_scale: float
+    norm_eps: float
+    decay_rank: int = 0
+    kind: str = "gated_linear_attention"
+
+
+@dataclass(frozen=True)
+class WkvSpec:
+    """Time mixing with state [heads, dim, dim] per request and the previous token's input
+    as further state.  Each of r, k, v, g, w reads h + (h_prev - h) * mu of its own;
+    decay w_t = exp(-exp(W_w2 tanh(W_w1 mix_w) + w0)) per key channel (inner size
+    ``decay_rank``, the checkpoint's when 0); o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t,
+    then S_t = diag(w_t) S_(t-1) + k_t v_t^T.  Each head's output is divided by its root
+    mean square, multiplied by a gain over all heads and by silu(W_g mix_g), projected."""
+    hidden: int
+    heads: int
+    dim: int
+    norm_eps: float
+    decay_rank: int = 0
+    kind: str = "wkv"
+
+
+@dataclass(frozen=True)
 class SwiGluSpec:
     hidden: int
     intermediate: int
+    # tensor names inside the part's prefix: gate, up, down
+    names: tuple = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
     kind: str = "swiglu"
 
 
@@ -140,6 +211,11 @@ class MoeSpec:
     shared_gated: bool        # its output scaled by sigmoid(x . w_gate)
     shared_name: str = "shared_expert"
     shared_gate_name: str = "shared_expert_gate"
+    # tensor names inside the part's prefix: the router's matrix, and one expert's
+    # prefix with {e} for its number followed by its gate, up and down matrices
+    router_name: str = "gate.weight"
+    expert_names: tuple = ("experts.{e}.gate_proj.weight", "experts.{e}.up_proj.weight",
+                           "experts.{e}.down_proj.weight")
     kind: str = "moe"
 
 
@@ -148,7 +224,8 @@ class LayerSpec:
     """One layer: its parts, and ``kind``, the arrangement they run in.  "pre_norm" is
     x += mixer(norm(x)); x += ffn(norm(x)); "sublayer_norm" is x += norm(mixer(x));
     x += norm(ffn(x)), where ``input_norm`` follows the mixer and ``post_norm`` the
-    feed-forward (``ffn`` and ``post_norm`` may be None: a layer without feed-forward)."""
+    feed-forward (``ffn`` and ``post_norm`` may be None: a layer without feed-forward);
+    "parallel" is x += mixer(input_norm(x)) + ffn(post_norm(x)), both of the same x."""
     prefix: str  # tensor-name prefix, e.g. "model.layers.3"
     input_norm: Any
     mixer: Any
@@ -166,13 +243,29 @@ class LayerSpec:
 
 
 @dataclass(frozen=True)
+class StreamAddSpec:
+    """Something added to the residual stream ahead of a run: row ``row`` of the tensor
+    ``table`` ([rows, width], by its checkpoint name) and, with ``embedding``, the stream
+    as it was before the first run (the embedding output) once more."""
+    table: Optional[str] = None
+    rows: int = 0
+    row: int = 0
+    embedding: bool = False
+
+
+@dataclass(frozen=True)
 class RunEntry:
     """One execution of a layer.  By default the run keeps its own cache (it writes
     this step's keys and values, then reads).  ``cache_of`` names a layer whose
     cache this run only reads: another layer's, or its own when the layer is run a
-    second time in the schedule and must see what its first run stored."""
+    second time in the schedule and must see what its first run stored.
+    ``cache_copy`` numbers caches of the same layer: a layer that runs several times
+    with the same weights, each run with a cache and state of its own, gives its runs
+    different numbers.  ``before`` is added to the stream ahead of the run."""
     layer: int
     cache_of: Optional[int] = None
+    cache_copy: int = 0
+    before: Optional[StreamAddSpec] = None
 
     @property
     def cache_layer(self) -> int:
@@ -196,3 +289,4 @@ class ModelSpec:
     final_norm_name: str = "model.norm"
     head_name: str = "lm_head.weight"
     embed_scale: float = 1.0     # the residual stream starts as embed[token] * embed_scale
+    embed_position: Any = None   # a position spec whose vector is added to the embedding

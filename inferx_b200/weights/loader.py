@@ -35,8 +35,17 @@ class WeightError(ValueError):
         self.wrong_shape = list(wrong_shape)
 
 
+def shapes_agree(declared, found) -> bool:
+    """A declared size of -1 stands for whatever the source holds."""
+    declared, found = tuple(declared), tuple(found)
+    return len(declared) == len(found) and all(d == f or d == -1
+                                               for d, f in zip(declared, found))
+
+
 @dataclass(frozen=True)
 class TensorDecl:
+    """``shape`` may hold -1 for a size that the checkpoint decides (a source that makes
+    tensors up, like ``RandomSource``, needs every size)."""
     name: str
     shape: Tuple[int, ...]
     keep: str = "param"    # "param" (run dtype) | "float32" | "int32"
@@ -169,6 +178,9 @@ class RandomSource(WeightSource):
             return torch.zeros(decl.shape, dtype=torch.float32, device=self.device)
         numel = 1
         for n in decl.shape:
+            if int(n) < 0:
+                raise WeightError(f"tensor '{decl.name}': a size left to the checkpoint "
+                                  f"({list(decl.shape)}) cannot be drawn at random")
             numel *= int(n)
         key = _name_seed(self.seed, decl.name)
         if self.device.type == "cuda":
@@ -213,7 +225,7 @@ def check(decls: Sequence[TensorDecl], source: WeightSource, where: str = "weigh
     for d in decls:
         if d.name in have:
             got = tuple(source.shape(d.name))
-            if got != tuple(d.shape):
+            if not shapes_agree(d.shape, got):
                 wrong.append((d.name, tuple(d.shape), got))
     if not (missing or unexpected or wrong):
         return
@@ -234,7 +246,7 @@ def materialize(decl: TensorDecl, source: WeightSource, run_dtype: torch.dtype,
                 device) -> torch.Tensor:
     """One tensor, on ``device``, in the element type its declaration asks for."""
     t = source.fetch(decl)
-    if tuple(t.shape) != tuple(decl.shape):
+    if not shapes_agree(decl.shape, t.shape):
         raise WeightError(f"tensor '{decl.name}': expected shape {list(decl.shape)}, "
                           f"found {list(t.shape)}", wrong_shape=[(decl.name, decl.shape, t.shape)])
     if decl.keep == "int32":

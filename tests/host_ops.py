@@ -94,7 +94,7 @@ def append_kv(k, v, k_cache, v_cache, slots):
 
 
 def paged_attention_generic(q, k_cache, v_cache, block_table, seq_of_token, positions, window,
-                            scale):
+                            scale, softcap=0.0):
     T, heads, hd = q.shape
     P, kvh, page, _ = k_cache.shape
     rep = heads // kvh
@@ -111,14 +111,16 @@ def paged_attention_generic(q, k_cache, v_cache, block_table, seq_of_token, posi
             keys = _f(k_cache[pages, kh, offs, :])
             vals = _f(v_cache[pages, kh, offs, :])
             sc = (keys @ _f(q[t, h])) * scale
+            if softcap > 0:
+                sc = softcap * torch.tanh(sc / softcap)
             p = torch.exp(sc - sc.max())
             out[t, h] = (p[:, None] * vals).sum(0) / p.sum()
     return out.to(q.dtype)
 
 
-def paged_attention(q, k_cache, v_cache, block_table, step, window, scale):
+def paged_attention(q, k_cache, v_cache, block_table, step, window, scale, softcap=0.0):
     return paged_attention_generic(q, k_cache, v_cache, block_table, step.seq_of_token,
-                                   step.positions, window, scale)
+                                   step.positions, window, scale, softcap)
 
 
 def router_topk(x, w, top_k, renormalize, scale, extra_w=None):
@@ -380,3 +382,105 @@ def gate_heads(o, proj, gate_off):
     H, T, D = o.shape
     g = _f(proj[:, gate_off:gate_off + H * D])
     return (_f(o).transpose(0, 1).reshape(T, H * D) / (1.0 + torch.exp(-g))).to(o.dtype)
+
+
+# ---------------------------------------------------------------------------------------
+# parts of decoders with a parallel arrangement, recurrent mixers and tied keys/values
+def embed_sinusoid(table, ids, positions, freq, scale):
+    x = _f(table)[ids.long()] * scale
+    a = positions.to(torch.float32)[:, None] * freq[None, :]
+    W = x.shape[1]
+    pos = torch.stack([torch.sin(a), torch.cos(a)], dim=-1).reshape(x.shape[0], -1)[:, :W]
+    return x + pos
+
+
+def add_rmsnorm_sum(resid, terms, vector, gains, eps, out_dtype, rows=None):
+    total = None
+    for t in terms:
+        if hasattr(t, "materialize"):
+            t = t.materialize()
+        total = _f(t) if total is None else total + _f(t)
+    if vector is not None:
+        total = vector[None, :].expand_as(resid) if total is None else total + vector
+    if rows is None:
+        if total is not None:
+            resid += total
+        v = resid
+    else:
+        v = resid[rows.long()]
+        if total is not None:
+            v = v + total[rows.long()]
+    ms = (v * v).sum(-1, keepdim=True) / v.shape[-1]
+    n = v * (1.0 / torch.sqrt(ms + eps))
+    return tuple((n * g).to(out_dtype) for g in gains)
+
+
+def qk_norm_append(qk, q_gain, k_gain, positions, heads, kv_heads, head_dim, eps, temp_coef,
+                   temp_every, k_cache, v_cache, slots):
+    T = qk.shape[0]
+    x = _f(qk)
+    q = x[:, :heads * head_dim].reshape(T, heads, head_dim)
+    k = x[:, heads * head_dim:].reshape(T, kv_heads, head_dim)
+
+    def unit(v):
+        return v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps)
+
+    qn = unit(q) * q_gain
+    if temp_every > 0:
+        p = positions.to(torch.float32)
+        qn = qn * (1.0 + temp_coef * torch.log(torch.floor((p + 1) / temp_every) + 1.0))[:, None, None]
+    if k_cache is not None:
+        _scatter(k_cache, unit(k) * k_gain, slots)
+        _scatter(v_cache, k, slots)
+    return qn.to(qk.dtype)
+
+
+def shift_mix(x, mu, state, step):
+    T, W = x.shape
+    out = torch.zeros(mu.shape[0], T, W)
+    for s in range(step.num_seqs):
+        a, b = int(step.cu_q[s]), int(step.cu_q[s + 1])
+        slot = int(step.state_slot[s])
+        h = _f(x[a:b])
+        prev = torch.cat([state[slot][None, :], h[:-1]], 0)
+        out[:, a:b] = h[None] + (prev - h)[None] * mu[:, None, :]
+        state[slot] = h[-1]
+    return out.to(x.dtype)
+
+
+def lowrank_decay(x, w2, b, mode, tau=1.0):
+    x = _f(x)
+    if mode == "exp_exp_tanh":
+        return torch.exp(-torch.exp(torch.tanh(x) @ w2.T + b))
+    assert mode == "sigmoid_root"
+    return torch.exp(torch.nn.functional.logsigmoid(x @ w2.T + b) / tau)
+
+
+def linear_recurrence(q, k, v, decay, bonus, state, step, heads, dim, vdim, q_scale=1.0,
+                      bonus_form=False):
+    T = q.shape[0]
+    qf = _f(q).reshape(T, heads, dim) * q_scale
+    kf, vf = _f(k).reshape(T, heads, dim), _f(v).reshape(T, heads, vdim)
+    w = decay.reshape(T, heads, dim)
+    out = torch.zeros(T, heads, vdim)
+    for s in range(step.num_seqs):
+        slot = int(step.state_slot[s])
+        S = state[slot].clone()
+        for t in range(int(step.cu_q[s]), int(step.cu_q[s + 1])):
+            kv = kf[t][:, :, None] * vf[t][:, None, :]
+            if bonus_form:
+                out[t] = torch.einsum("hkv,hk->hv", S + bonus[:, :, None] * kv, qf[t])
+                S = w[t][:, :, None] * S + kv
+            else:
+                S = w[t][:, :, None] * S + kv
+                out[t] = torch.einsum("hkv,hk->hv", S, qf[t])
+        state[slot] = S
+    return out
+
+
+def head_norm_gate(o, weight, gate, eps, out_dtype):
+    T, H, V = o.shape
+    n = o / torch.sqrt((o * o).mean(-1, keepdim=True) + eps)
+    n = n * (weight.reshape(H, V) if weight.numel() == H * V else weight)
+    g = _f(gate).reshape(T, H, V)
+    return (n * (g / (1.0 + torch.exp(-g)))).reshape(T, H * V).to(out_dtype)
