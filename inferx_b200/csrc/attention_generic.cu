@@ -26,7 +26,7 @@ paged_attention_generic_kernel(const TA* __restrict__ q, const TA* __restrict__ 
                                const int* __restrict__ seq_of_token,
                                const int* __restrict__ positions, TA* __restrict__ out, int heads,
                                int kvh, int hd, int page_size, int max_blocks, int window,
-                               float scale) {
+                               float scale, float softcap) {
   extern __shared__ float smem[];
   float* qs = smem;        // [hd]
   float* sc = smem + hd;   // [ATT_TILE]
@@ -60,7 +60,10 @@ paged_attention_generic_kernel(const TA* __restrict__ q, const TA* __restrict__ 
       float dot = 0.f;
       for (int d = lane; d < hd; d += 32) dot += qs[d] * to_f32(krow[d]);
       dot = warp_sum(dot);
-      if (lane == 0) sc[j] = dot * scale;
+      if (lane == 0) {
+        const float sv = dot * scale;
+        sc[j] = softcap > 0.f ? softcap * tanhf(sv / softcap) : sv;   // squashed scores
+      }
     }
     __syncthreads();
     float tm = -INFINITY;
@@ -107,7 +110,7 @@ IX_API int ix_paged_attention_generic(const void* q, const void* k_cache, const 
                                       const int* block_table, const int* seq_of_token,
                                       const int* positions, void* out, int act_dtype, int T,
                                       int heads, int kvh, int hd, int page_size, int max_blocks,
-                                      int window, float scale, cudaStream_t stream) {
+                                      int window, float scale, float softcap, cudaStream_t stream) {
   if (T <= 0) return IX_OK;
   if (heads <= 0 || kvh <= 0 || heads % kvh != 0 || page_size <= 0 || max_blocks <= 0)
     return IX_ERR_SIZE;
@@ -120,6 +123,6 @@ IX_API int ix_paged_attention_generic(const void* q, const void* k_cache, const 
                     (paged_attention_generic_kernel<TA><<<grid, ATT_THREADS, smem, stream>>>(
                         (const TA*)q, (const TA*)k_cache, (const TA*)v_cache, block_table,
                         seq_of_token, positions, (TA*)out, heads, kvh, hd, page_size, max_blocks,
-                        window, scale)));
+                        window, scale, softcap)));
   return ix_launch_status();
 }

@@ -50,7 +50,8 @@ paged_attention_tiled_kernel(const TA* __restrict__ q, const TA* __restrict__ kc
                              const TA* __restrict__ vc, const int* __restrict__ block_table,
                              const int* __restrict__ cu_q, const int* __restrict__ q_pos0,
                              TA* __restrict__ out, int S, int heads, int kvh, int hd,
-                             int page_size, int max_blocks, int window, float scale) {
+                             int page_size, int max_blocks, int window, float scale,
+                             float softcap) {
   extern __shared__ __align__(16) float tsm[];
   const int ld = hd + 4;                         // row pitch: 16-byte rows, no bank conflicts
   float* Qs = tsm;                               // [TA_BQ][ld]
@@ -156,7 +157,9 @@ paged_attention_tiled_kernel(const TA* __restrict__ q, const TA* __restrict__ kc
       for (int j = 0; j < 4; ++j) {
         const int kp = kv0 + sk + 16 * j;
         const bool seen = r < rows_valid && kp <= qp && kp >= first;
-        sc[i][j] = seen ? sc[i][j] * scale : -INFINITY;
+        float sv = sc[i][j] * scale;
+        if (softcap > 0.f) sv = softcap * tanhf(sv / softcap);   // squashed scores
+        sc[i][j] = seen ? sv : -INFINITY;
         tm = fmaxf(tm, sc[i][j]);
       }
 #pragma unroll
@@ -236,7 +239,7 @@ IX_API int ix_paged_attention_tiled(const void* q, const void* k_cache, const vo
                                     const int* block_table, const int* cu_q, const int* q_pos0,
                                     void* out, int act_dtype, int T, int S, int heads, int kvh,
                                     int hd, int page_size, int max_blocks, int window,
-                                    float scale, cudaStream_t stream) {
+                                    float scale, float softcap, cudaStream_t stream) {
   if (T <= 0) return IX_OK;
   if (S <= 0 || heads <= 0 || kvh <= 0 || heads % kvh != 0 || page_size <= 0 || max_blocks <= 0 ||
       window < 0)
@@ -258,7 +261,8 @@ IX_API int ix_paged_attention_tiled(const void* q, const void* k_cache, const vo
     }
     kern<<<grid, TA_THREADS, smem, stream>>>((const TA*)q, (const TA*)k_cache, (const TA*)v_cache,
                                              block_table, cu_q, q_pos0, (TA*)out, S, heads, kvh,
-                                             hd, page_size, max_blocks, window, scale);
+                                             hd, page_size, max_blocks, window, scale,
+                                             softcap);
   });
   return ix_launch_status();
 }

@@ -1,0 +1,174 @@
+// Row-wise kernels for decoders whose layers read one row of the residual stream through
+// two norms at once, add a position vector to the embedding, or norm queries and keys
+// per head:
+//
+//   embedding + sinusoid    out[t] = table[id[t]] * scale + pos(p[t]); entry 2i of pos is
+//                           sin(p * f[i]), entry 2i+1 cos(p * f[i])
+//   sum + RMS norm          x[r] += d0[r] + d1[r] + d2[r] + vec, then up to two normed views
+//                           of the same row, out_j = x * inv * gain_j (or gathered rows
+//                           without writing the stream back)
+//   q/k norm + cache write  per head RMS norm of q and k with a gain shared by the heads,
+//                           q times a temperature of the position, normed k into the key
+//                           pages and k as projected into the value pages
+//
+// All arithmetic is fp32 with the accurate library functions; the residual stream is fp32.
+#include "common.cuh"
+
+__device__ __forceinline__ float load_any(const void* p, int code, size_t i) {
+  return code == IX_F32 ? reinterpret_cast<const float*>(p)[i]
+                        : __bfloat162float(reinterpret_cast<const bf16*>(p)[i]);
+}
+
+// ---------------------------------------------------------------------------
+template <typename TT>
+__global__ void embed_sinusoid_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
+                                      const int* __restrict__ positions,
+                                      const float* __restrict__ freq, float* __restrict__ out,
+                                      int W, float scale) {
+  IX_PDL_WAIT();
+  const int t = blockIdx.x;
+  const TT* row = table + (size_t)ids[t] * W;
+  const float p = (float)positions[t];
+  float* o = out + (size_t)t * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float a = p * freq[i >> 1];
+    const float pe = (i & 1) ? cosf(a) : sinf(a);
+    o[i] = to_f32(row[i]) * scale + pe;
+  }
+}
+
+IX_API int ix_embed_sinusoid(const void* table, int table_dtype, const int* ids,
+                             const int* positions, const float* freq, int T, int W, int V,
+                             float* out, float scale, cudaStream_t stream) {
+  if (T <= 0) return IX_OK;
+  if (W <= 0 || V <= 0) return IX_ERR_SIZE;
+  const int threads = W >= 1024 ? 256 : 128;
+  IX_DISPATCH_DTYPE(table_dtype, TT,
+                    ix_launch(embed_sinusoid_kernel<TT>, dim3(T), dim3(threads), 0, stream,
+                              (const TT*)table, ids, positions, freq, out, W, scale));
+  return ix_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// sum + RMS norm.  One block per output row; the row is kept in shared memory between
+// the pass that sums and the pass that scales.
+// ---------------------------------------------------------------------------
+template <typename TA>
+__global__ void add_rmsnorm_sum_kernel(float* __restrict__ resid, const void* __restrict__ d0,
+                                       int c0, const void* __restrict__ d1, int c1,
+                                       const void* __restrict__ d2, int c2,
+                                       const float* __restrict__ vec,
+                                       const int* __restrict__ rows,
+                                       const float* __restrict__ g0,
+                                       const float* __restrict__ g1, TA* __restrict__ out0,
+                                       TA* __restrict__ out1, int W, float eps, int write_back) {
+  extern __shared__ float row[];
+  __shared__ float scratch[32];
+  IX_PDL_WAIT();
+  const int r = blockIdx.x;
+  const size_t src = (size_t)(rows ? rows[r] : r) * W;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float add = 0.f;
+    bool any = false;
+    if (d0) { add = load_any(d0, c0, src + i); any = true; }
+    if (d1) { add = any ? add + load_any(d1, c1, src + i) : load_any(d1, c1, src + i); any = true; }
+    if (d2) { add = any ? add + load_any(d2, c2, src + i) : load_any(d2, c2, src + i); any = true; }
+    if (vec) { add = any ? add + vec[i] : vec[i]; any = true; }
+    float v = resid[src + i];
+    if (any) {
+      v += add;
+      if (write_back) resid[src + i] = v;
+    }
+    row[i] = v;
+    ss += v * v;
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)W + eps);
+  const size_t dst = (size_t)r * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float n = row[i] * inv;
+    out0[dst + i] = from_f32<TA>(n * g0[i]);
+    if (out1) out1[dst + i] = from_f32<TA>(n * g1[i]);
+  }
+}
+
+IX_API int ix_add_rmsnorm_sum(float* resid, const void* d0, int c0, const void* d1, int c1,
+                              const void* d2, int c2, const float* vec, const int* rows,
+                              const float* g0, const float* g1, void* out0, void* out1,
+                              int out_dtype, int R, int W, float eps, int write_back,
+                              cudaStream_t stream) {
+  if (R <= 0) return IX_OK;
+  if (W <= 0 || !g0 || !out0 || (out1 && !g1)) return IX_ERR_SIZE;
+  const size_t smem = (size_t)W * sizeof(float);
+  if (smem > 200 * 1024) return IX_ERR_SMEM;
+  const int threads = W >= 2048 ? 512 : (W >= 512 ? 256 : 128);
+  IX_DISPATCH_DTYPE(out_dtype, TA, {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(add_rmsnorm_sum_kernel<TA>,
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ix_launch(add_rmsnorm_sum_kernel<TA>, dim3(R), dim3(threads), smem, stream, resid, d0, c0, d1,
+              c1, d2, c2, vec, rows, g0, g1, (TA*)out0, (TA*)out1, W, eps, write_back);
+  });
+  return ix_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// q/k norm + cache write.  One warp per (token, head); heads 0..H-1 are queries, the
+// following G are key/value heads.  qk row layout: [H * D | G * D].
+// ---------------------------------------------------------------------------
+#define QKN_WARPS 4
+
+template <typename TA>
+__global__ void qk_norm_append_kernel(const TA* __restrict__ qk, const float* __restrict__ q_gain,
+                                      const float* __restrict__ k_gain,
+                                      const int* __restrict__ positions, TA* __restrict__ q_out,
+                                      TA* __restrict__ k_cache, TA* __restrict__ v_cache,
+                                      const int* __restrict__ slots, int H, int G, int D,
+                                      int page_size, float eps, float temp_coef, int temp_every) {
+  IX_PDL_WAIT();
+  const int t = blockIdx.x;
+  const int j = blockIdx.y * QKN_WARPS + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (j >= H + G) return;
+  const TA* src = qk + (size_t)t * (H + G) * D + (size_t)j * D;
+  float ss = 0.f;
+  for (int d = lane; d < D; d += 32) {
+    const float v = to_f32(src[d]);
+    ss += v * v;
+  }
+  const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)D + eps);
+  if (j < H) {
+    float temp = 1.0f;
+    if (temp_every > 0)
+      temp = 1.0f + temp_coef * logf((float)((positions[t] + 1) / temp_every) + 1.0f);
+    TA* dst = q_out + ((size_t)t * H + j) * D;
+    for (int d = lane; d < D; d += 32)
+      dst[d] = from_f32<TA>(to_f32(src[d]) * inv * q_gain[d] * temp);
+  } else if (k_cache) {
+    const int g = j - H;
+    const int slot = slots[t];
+    if (slot < 0) return;
+    const size_t base = (((size_t)(slot / page_size) * G + g) * page_size + slot % page_size) * D;
+    for (int d = lane; d < D; d += 32) {
+      v_cache[base + d] = src[d];
+      k_cache[base + d] = from_f32<TA>(to_f32(src[d]) * inv * k_gain[d]);
+    }
+  }
+}
+
+IX_API int ix_qk_norm_append(const void* qk, int dtype, const float* q_gain, const float* k_gain,
+                             const int* positions, void* q_out, void* k_cache, void* v_cache,
+                             const int* slots, int T, int H, int G, int D, int page_size,
+                             float eps, float temp_coef, int temp_every, cudaStream_t stream) {
+  if (T <= 0) return IX_OK;
+  if (H <= 0 || G <= 0 || D <= 0 || page_size <= 0 || temp_every < 0) return IX_ERR_SIZE;
+  if ((k_cache != nullptr) != (v_cache != nullptr) || (k_cache && !slots)) return IX_ERR_SIZE;
+  const int groups = (H + G + QKN_WARPS - 1) / QKN_WARPS;
+  if (groups > 65535) return IX_ERR_SIZE;
+  IX_DISPATCH_DTYPE(dtype, TA,
+                    ix_launch(qk_norm_append_kernel<TA>, dim3(T, groups), dim3(32 * QKN_WARPS), 0,
+                              stream, (const TA*)qk, q_gain, k_gain, positions, (TA*)q_out,
+                              (TA*)k_cache, (TA*)v_cache, slots, H, G, D, page_size, eps,
+                              temp_coef, temp_every));
+  return ix_launch_status();
+}

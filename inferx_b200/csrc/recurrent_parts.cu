@@ -1,0 +1,318 @@
+// Kernels of mixers that carry a matrix of state per head and request:
+//
+//   shift mix          out[m][t] = x[t] + (x[t-1] - x[t]) * mu[m] for several mu at once;
+//                      the row before a sequence's first token of the step comes from
+//                      per-request state, which then takes the sequence's last row
+//   low-rank decay     z[t][c] = b[c] + sum_r act(x[t][r]) * w2[c][r], then
+//                        form 0:  exp(-exp(z)),            act = tanh
+//                        form 1:  sigmoid(z)^(1/tau),       act = identity
+//   linear recurrence  per (sequence, head), tokens in order, S [K][V] in fp32:
+//                        plain form:  S = diag(w_t) S + k_t v_t^T;  o_t = S^T q_t
+//                        bonus form:  o_t = (S + diag(u) k_t v_t^T)^T q_t;
+//                                     S = diag(w_t) S + k_t v_t^T
+//   head norm + gate   out[t][h] = o[t][h] / rms(o[t][h]) * gain * silu(gate[t][h])
+//
+// Everything is computed in fp32 with the accurate library functions; inputs that are
+// projections arrive in the run's element type.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// shift mix.  One block per token.  The block of a sequence's first token reads the
+// state row and afterwards stores the sequence's last row of this step there; each
+// thread touches the same elements in both, so the read precedes the write.
+// ---------------------------------------------------------------------------
+template <typename TA>
+__global__ void shift_mix_kernel(const TA* __restrict__ x, const float* __restrict__ mu,
+                                 float* __restrict__ state, const int* __restrict__ cu_q,
+                                 const int* __restrict__ seq_of_token,
+                                 const int* __restrict__ state_slot, TA* __restrict__ out, int T,
+                                 int W, int n_mix) {
+  IX_PDL_WAIT();
+  const int t = blockIdx.x;
+  const int s = seq_of_token[t];
+  const bool first = (t == cu_q[s]);
+  const TA* cur = x + (size_t)t * W;
+  float* st = state + (size_t)state_slot[s] * W;
+  const TA* last = x + (size_t)(cu_q[s + 1] - 1) * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = to_f32(cur[i]);
+    const float p = first ? st[i] : to_f32(cur[i - W]);
+    const float d = p - v;
+    for (int m = 0; m < n_mix; ++m)
+      out[((size_t)m * T + t) * W + i] = from_f32<TA>(v + d * mu[(size_t)m * W + i]);
+    if (first) st[i] = to_f32(last[i]);
+  }
+}
+
+IX_API int ix_shift_mix(const void* x, int dtype, const float* mu, float* state, const int* cu_q,
+                        const int* seq_of_token, const int* state_slot, void* out, int T, int W,
+                        int n_mix, cudaStream_t stream) {
+  if (T <= 0) return IX_OK;
+  if (W <= 0 || n_mix <= 0) return IX_ERR_SIZE;
+  const int threads = W >= 1024 ? 256 : 128;
+  IX_DISPATCH_DTYPE(dtype, TA,
+                    ix_launch(shift_mix_kernel<TA>, dim3(T), dim3(threads), 0, stream,
+                              (const TA*)x, mu, state, cu_q, seq_of_token, state_slot, (TA*)out,
+                              T, W, n_mix));
+  return ix_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// low-rank decay.  A block takes LRD_TOKENS tokens and LRD_THREADS channels; a thread
+// reads its channel's row of w2 once for all of the block's tokens.  A token's sum runs
+// over r in ascending order whatever else is in the block.
+// ---------------------------------------------------------------------------
+#define LRD_TOKENS 8
+#define LRD_THREADS 128
+
+template <typename TX>
+__global__ void lowrank_decay_kernel(const TX* __restrict__ x, long long ldx,
+                                     const float* __restrict__ w2, const float* __restrict__ b,
+                                     float* __restrict__ out, int T, int C, int R, int form,
+                                     float inv_tau) {
+  extern __shared__ float act[];   // [LRD_TOKENS][R]
+  IX_PDL_WAIT();
+  const int t0 = blockIdx.x * LRD_TOKENS;
+  const int nt = min(LRD_TOKENS, T - t0);
+  for (int i = threadIdx.x; i < nt * R; i += blockDim.x) {
+    const float v = to_f32(x[(size_t)(t0 + i / R) * ldx + i % R]);
+    act[i] = form == 0 ? tanhf(v) : v;
+  }
+  __syncthreads();
+  const int c = blockIdx.y * LRD_THREADS + threadIdx.x;
+  if (c >= C) return;
+  float z[LRD_TOKENS];
+#pragma unroll
+  for (int j = 0; j < LRD_TOKENS; ++j) z[j] = 0.f;
+  const float* wr = w2 + (size_t)c * R;
+  for (int r = 0; r < R; ++r) {
+    const float w = wr[r];
+#pragma unroll
+    for (int j = 0; j < LRD_TOKENS; ++j)
+      if (j < nt) z[j] += act[j * R + r] * w;
+  }
+  const float bias = b ? b[c] : 0.f;
+#pragma unroll
+  for (int j = 0; j < LRD_TOKENS; ++j) {
+    if (j >= nt) break;
+    const float v = z[j] + bias;
+    float d;
+    if (form == 0) {
+      d = expf(-expf(v));
+    } else {
+      // log sigmoid(v) = min(v, 0) - log(1 + exp(-|v|))
+      d = expf((fminf(v, 0.f) - log1pf(expf(-fabsf(v)))) * inv_tau);
+    }
+    out[(size_t)(t0 + j) * C + c] = d;
+  }
+}
+
+IX_API int ix_lowrank_decay(const void* x, int x_dtype, long long ldx, const float* w2,
+                            const float* b, float* out, int T, int C, int R, int form, float tau,
+                            cudaStream_t stream) {
+  if (T <= 0) return IX_OK;
+  if (C <= 0 || R <= 0 || ldx < R || (form != 0 && form != 1) || !(tau > 0.f)) return IX_ERR_SIZE;
+  const size_t smem = (size_t)LRD_TOKENS * R * sizeof(float);
+  if (smem > 48 * 1024) return IX_ERR_SMEM;
+  dim3 grid((T + LRD_TOKENS - 1) / LRD_TOKENS, (C + LRD_THREADS - 1) / LRD_THREADS);
+  if (grid.y > 65535) return IX_ERR_SIZE;
+  IX_DISPATCH_DTYPE(x_dtype, TX,
+                    ix_launch(lowrank_decay_kernel<TX>, grid, dim3(LRD_THREADS), smem, stream,
+                              (const TX*)x, ldx, w2, b, out, T, C, R, form, 1.0f / tau));
+  return ix_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// linear recurrence.  grid (ceil(V / 32), heads, sequences); a block is 32 value columns
+// times KS slices of the key channels (one warp per slice).  A thread keeps its KPT
+// entries of one state column in registers from the sequence's first token of the step
+// to its last; key channels do not interact, so the slices walk a chunk of tokens without
+// meeting, leave their partial outputs in shared memory, and the partials are added in
+// ascending slice order.  The order of every sum is fixed by (K, KS) alone: a position's
+// output does not depend on how its sequence was cut into steps or chunks.
+// ---------------------------------------------------------------------------
+#define LR_COLS 32
+#define LR_CHUNK 16
+
+template <typename TA, int KPT, bool BONUS>
+__global__ void __launch_bounds__(LR_COLS * 8)
+linear_recurrence_kernel(const TA* __restrict__ q, long long ldq, const TA* __restrict__ k,
+                         long long ldk, const TA* __restrict__ v, long long ldv,
+                         const float* __restrict__ decay, const float* __restrict__ bonus,
+                         float* __restrict__ state, const int* __restrict__ cu_q,
+                         const int* __restrict__ state_slot, float* __restrict__ out, int H,
+                         int K, int V, int KS, float q_scale) {
+  extern __shared__ float sm[];
+  float* q_s = sm;                       // [LR_CHUNK][K]
+  float* k_s = q_s + LR_CHUNK * K;       // [LR_CHUNK][K]
+  float* w_s = k_s + LR_CHUNK * K;       // [LR_CHUNK][K]
+  float* v_s = w_s + LR_CHUNK * K;       // [LR_CHUNK][LR_COLS]
+  float* part = v_s + LR_CHUNK * LR_COLS;  // [KS][LR_CHUNK][LR_COLS]
+  IX_PDL_WAIT();
+  const int lane = threadIdx.x & 31, ks = threadIdx.x >> 5;
+  const int v0 = blockIdx.x * LR_COLS, h = blockIdx.y, s = blockIdx.z;
+  const int col = v0 + lane;
+  const bool col_ok = col < V;
+  const int t_begin = cu_q[s], t_end = cu_q[s + 1];
+  float* st = state + ((size_t)state_slot[s] * H + h) * K * V;
+  const int kk0 = ks * KPT;
+
+  float S[KPT], u[KPT];
+#pragma unroll
+  for (int i = 0; i < KPT; ++i) {
+    const int kk = kk0 + i;
+    S[i] = (kk < K && col_ok) ? st[(size_t)kk * V + col] : 0.f;
+    u[i] = (BONUS && kk < K) ? bonus[(size_t)h * K + kk] : 0.f;
+  }
+
+  for (int t0 = t_begin; t0 < t_end; t0 += LR_CHUNK) {
+    const int n = min(LR_CHUNK, t_end - t0);
+    for (int i = threadIdx.x; i < n * K; i += blockDim.x) {
+      const int c = i / K, kk = i % K;
+      const size_t t = (size_t)(t0 + c);
+      q_s[i] = to_f32(q[t * ldq + (size_t)h * K + kk]) * q_scale;
+      k_s[i] = to_f32(k[t * ldk + (size_t)h * K + kk]);
+      w_s[i] = decay[(t * H + h) * K + kk];
+    }
+    for (int i = threadIdx.x; i < n * LR_COLS; i += blockDim.x) {
+      const int c = i / LR_COLS, j = i % LR_COLS;
+      v_s[i] = (v0 + j < V) ? to_f32(v[(size_t)(t0 + c) * ldv + (size_t)h * V + v0 + j]) : 0.f;
+    }
+    __syncthreads();
+    for (int c = 0; c < n; ++c) {
+      const float vj = v_s[c * LR_COLS + lane];
+      const float* qc = q_s + c * K + kk0;
+      const float* kc = k_s + c * K + kk0;
+      const float* wc = w_s + c * K + kk0;
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < KPT; ++i) {
+        if (kk0 + i < K) {
+          const float kv = kc[i] * vj;
+          if (BONUS) {
+            acc += (S[i] + u[i] * kv) * qc[i];
+            S[i] = wc[i] * S[i] + kv;
+          } else {
+            S[i] = wc[i] * S[i] + kv;
+            acc += S[i] * qc[i];
+          }
+        }
+      }
+      part[(ks * LR_CHUNK + c) * LR_COLS + lane] = acc;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n * LR_COLS; i += blockDim.x) {
+      const int c = i / LR_COLS, j = i % LR_COLS;
+      if (v0 + j < V) {
+        float total = 0.f;
+        for (int w = 0; w < KS; ++w) total += part[(w * LR_CHUNK + c) * LR_COLS + j];
+        out[((size_t)(t0 + c) * H + h) * V + v0 + j] = total;
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < KPT; ++i) {
+    const int kk = kk0 + i;
+    if (kk < K && col_ok) st[(size_t)kk * V + col] = S[i];
+  }
+}
+
+IX_API int ix_linear_recurrence_max_dim() { return 8 * 64; }
+
+template <typename TA, int KPT>
+static void launch_recurrence(const void* q, long long ldq, const void* k, long long ldk,
+                              const void* v, long long ldv, const float* decay,
+                              const float* bonus, float* state, const int* cu_q,
+                              const int* state_slot, float* out, int S, int H, int K, int V,
+                              int KS, float q_scale, int bonus_form, size_t smem,
+                              cudaStream_t stream) {
+  dim3 grid((V + LR_COLS - 1) / LR_COLS, H, S), block(LR_COLS * KS);
+  if (bonus_form) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(linear_recurrence_kernel<TA, KPT, true>,
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ix_launch(linear_recurrence_kernel<TA, KPT, true>, grid, block, smem, stream, (const TA*)q,
+              ldq, (const TA*)k, ldk, (const TA*)v, ldv, decay, bonus, state, cu_q, state_slot,
+              out, H, K, V, KS, q_scale);
+  } else {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(linear_recurrence_kernel<TA, KPT, false>,
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ix_launch(linear_recurrence_kernel<TA, KPT, false>, grid, block, smem, stream, (const TA*)q,
+              ldq, (const TA*)k, ldk, (const TA*)v, ldv, decay, bonus, state, cu_q, state_slot,
+              out, H, K, V, KS, q_scale);
+  }
+}
+
+IX_API int ix_linear_recurrence(const void* q, long long ldq, const void* k, long long ldk,
+                                const void* v, long long ldv, int dtype, const float* decay,
+                                const float* bonus, float* state, const int* cu_q,
+                                const int* state_slot, float* out, int S, int H, int K, int V,
+                                float q_scale, int bonus_form, cudaStream_t stream) {
+  if (S <= 0) return IX_OK;
+  if (H <= 0 || K <= 0 || V <= 0 || K > 8 * 64 || H > 65535 || S > 65535) return IX_ERR_SIZE;
+  if (bonus_form && !bonus) return IX_ERR_SIZE;
+  const int KS = K > 32 ? 8 : (K > 8 ? 4 : 1);
+  const int kpt = (K + KS - 1) / KS;
+  const size_t smem =
+      ((size_t)3 * LR_CHUNK * K + LR_CHUNK * LR_COLS + (size_t)KS * LR_CHUNK * LR_COLS) *
+      sizeof(float);
+  if (smem > 200 * 1024) return IX_ERR_SMEM;
+#define LR_GO(KPT)                                                                              \
+  IX_DISPATCH_DTYPE(dtype, TA,                                                                  \
+                    (launch_recurrence<TA, KPT>(q, ldq, k, ldk, v, ldv, decay, bonus, state,    \
+                                                cu_q, state_slot, out, S, H, K, V, KS, q_scale, \
+                                                bonus_form, smem, stream)))
+  if (kpt <= 8) LR_GO(8);
+  else if (kpt <= 16) LR_GO(16);
+  else if (kpt <= 32) LR_GO(32);
+  else LR_GO(64);
+#undef LR_GO
+  return ix_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// head norm + gate.  One warp per (token, head).  `gain` covers all heads
+// (gain_per_head) or is shared by them.
+// ---------------------------------------------------------------------------
+#define HNG_WARPS 4
+
+template <typename TG, typename TA>
+__global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ gain,
+                                      int gain_per_head, const TG* __restrict__ gate,
+                                      long long ldg, TA* __restrict__ out, int H, int V,
+                                      float eps) {
+  IX_PDL_WAIT();
+  const int t = blockIdx.x;
+  const int h = blockIdx.y * HNG_WARPS + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (h >= H) return;
+  const float* row = o + ((size_t)t * H + h) * V;
+  float ss = 0.f;
+  for (int c = lane; c < V; c += 32) ss += row[c] * row[c];
+  const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)V + eps);
+  const float* g = gain + (gain_per_head ? (size_t)h * V : 0);
+  const TG* gt = gate + (size_t)t * ldg + (size_t)h * V;
+  TA* dst = out + ((size_t)t * H + h) * V;
+  for (int c = lane; c < V; c += 32) {
+    const float z = to_f32(gt[c]);
+    dst[c] = from_f32<TA>(row[c] * inv * g[c] * (z / (1.0f + expf(-z))));
+  }
+}
+
+IX_API int ix_head_norm_gate(const float* o, const float* gain, int gain_per_head,
+                             const void* gate, int gate_dtype, long long ldg, void* out,
+                             int out_dtype, int T, int H, int V, float eps,
+                             cudaStream_t stream) {
+  if (T <= 0) return IX_OK;
+  if (H <= 0 || V <= 0 || ldg < (long long)H * V) return IX_ERR_SIZE;
+  const int groups = (H + HNG_WARPS - 1) / HNG_WARPS;
+  if (groups > 65535) return IX_ERR_SIZE;
+  if (gate_dtype != out_dtype) return IX_ERR_UNSUPPORTED;
+  IX_DISPATCH_DTYPE(out_dtype, TA,
+                    ix_launch(head_norm_gate_kernel<TA, TA>, dim3(T, groups),
+                              dim3(32 * HNG_WARPS), 0, stream, o, gain, gain_per_head,
+                              (const TA*)gate, ldg, (TA*)out, H, V, eps));
+  return ix_launch_status();
+}

@@ -122,13 +122,14 @@ def set_dependent_launch(on: bool) -> None:
 # Sizes the kernels refuse.  Parts call these when a model is built, so that a model the
 # kernels cannot run is refused with the offending size named, before weights are read;
 # the kernels' own checks remain (they return "a size this kernel does not take").
-def check_attention_limits(heads: int, kv_heads: int, head_dim: int, dtype, where: str = ""):
+def check_attention_limits(heads: int, kv_heads: int, head_dim: int, dtype, where: str = "",
+                           allow_odd: bool = False):
     lib = _lib()
     most = lib.ix_attention_max_head_dim()
     if head_dim > most:
         raise KernelError(f"{where}: head size {head_dim} exceeds the largest the attention "
                           f"kernels take ({most})")
-    if head_dim % 2:
+    if head_dim % 2 and not allow_odd:
         raise KernelError(f"{where}: head size {head_dim} is odd")
     if heads > 65535 or heads % max(1, kv_heads):
         raise KernelError(f"{where}: {heads} heads over {kv_heads} key/value heads is not a "
@@ -382,7 +383,8 @@ def qkv_project_rope_append(x: torch.Tensor, w: torch.Tensor, bias: Optional[tor
 
 def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                             block_table: torch.Tensor, seq_of_token: torch.Tensor,
-                            positions: torch.Tensor, window: int, scale: float):
+                            positions: torch.Tensor, window: int, scale: float,
+                            softcap: float = 0.0):
     _chk("q", q)
     _chk("k_cache", k_cache, q.dtype)
     _chk("v_cache", v_cache, q.dtype)
@@ -397,7 +399,7 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
     code = _lib().ix_paged_attention_generic(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(seq_of_token),
         _ptr(positions), _ptr(out), _dtype_code(q), T, heads, kvh, hd, page,
-        block_table.shape[1], window, ctypes.c_float(scale), _stream())
+        block_table.shape[1], window, ctypes.c_float(scale), ctypes.c_float(softcap), _stream())
     _check(code, "paged_attention_generic")
     _count()
     return out
@@ -405,7 +407,7 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
 
 def paged_attention_tiled(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                           block_table: torch.Tensor, cu_q: torch.Tensor, q_pos0: torch.Tensor,
-                          window: int, scale: float):
+                          window: int, scale: float, softcap: float = 0.0):
     """CUDA-core attention for a ragged batch, tiled (32 queries of a sequence against 64
     keys at a time in shared memory, fp32 math): sequence s brings the queries
     q[cu_q[s]:cu_q[s+1]] at positions q_pos0[s], q_pos0[s]+1, ...  Any element type, head
@@ -427,7 +429,7 @@ def paged_attention_tiled(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch
     code = _lib().ix_paged_attention_tiled(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(cu_q), _ptr(q_pos0),
         _ptr(out), _dtype_code(q), T, S, heads, kvh, hd, page, block_table.shape[1], window,
-        ctypes.c_float(scale), _stream())
+        ctypes.c_float(scale), ctypes.c_float(softcap), _stream())
     _check(code, "paged_attention_tiled")
     _count()
     return out
@@ -761,14 +763,19 @@ def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
 
 
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
-                    block_table: torch.Tensor, step, window: int, scale: float):
-    """Causal attention of this step's queries over the paged cache.
+                    block_table: torch.Tensor, step, window: int, scale: float,
+                    softcap: float = 0.0):
+    """Causal attention of this step's queries over the paged cache.  With ``softcap``
+    > 0 a score s becomes softcap * tanh(s / softcap) before the softmax.
 
     ``step`` carries the batch description (``seq_of_token``, ``positions``, ``cu_q``,
     ``q_pos0``, ``kv_len``, ``max_q_len``, ``max_kv_len``, ``all_decode``).  Steps of
     single tokens go to the split-KV kernel; everything else, and head sizes the
     tuned kernels do not take, to the general kernel."""
     hd = q.shape[2]
+    if softcap > 0:
+        return _paged_attention_softcap(q, k_cache, v_cache, block_table, step, window, scale,
+                                        softcap)
     if step.all_decode and hd in _DECODE_HEAD_SIZES.get(q.dtype, ()):
         return paged_attention_decode(q, k_cache, v_cache, block_table, step.kv_len,
                                       step.max_kv_len, window, scale)
@@ -793,6 +800,18 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                                      window, scale)
     return paged_attention_generic(q, k_cache, v_cache, block_table, step.seq_of_token,
                                    step.positions, window, scale)
+
+
+def _paged_attention_softcap(q, k_cache, v_cache, block_table, step, window, scale, softcap):
+    """Attention with squashed scores: the fp32-arithmetic kernels."""
+    hd = q.shape[2]
+    if (step.num_tokens >= TILED_ATTENTION_MIN_QUERIES * step.num_seqs
+            and _lib().ix_paged_attention_tiled_applies(hd)
+            and getattr(step, "cu_q", None) is not None):
+        return paged_attention_tiled(q, k_cache, v_cache, block_table, step.cu_q, step.q_pos0,
+                                     window, scale, softcap)
+    return paged_attention_generic(q, k_cache, v_cache, block_table, step.seq_of_token,
+                                   step.positions, window, scale, softcap)
 
 
 USE_TCGEN05 = True           # prompt-sized grouped products go to the tcgen05 kernel
@@ -1237,5 +1256,213 @@ def gate_heads(o: torch.Tensor, proj: torch.Tensor, gate_off: int):
     _check(_lib().ix_gate_heads(_ptr(o), ctypes.c_void_p(gate.data_ptr()),
                                 ctypes.c_longlong(proj.shape[1]), _ptr(out), _dtype_code(o), T, H,
                                 D, _stream()), "gate_heads")
+    _count()
+    return out
+
+
+# ---------------------------------------------------------------------------
+# Parts of decoders with a parallel arrangement, recurrent mixers and tied keys/values
+# ---------------------------------------------------------------------------
+def embed_sinusoid(table: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor,
+                   freq: torch.Tensor, scale: float = 1.0):
+    """out[t] = table[ids[t]] * scale + pos(positions[t]) in fp32; entry 2i of pos(p) is
+    sin(p * freq[i]), entry 2i+1 cos(p * freq[i])."""
+    _chk("table", table)
+    _chk("ids", ids, torch.int32)
+    _chk("positions", positions, torch.int32)
+    _chk("freq", freq, torch.float32)
+    V, W = table.shape
+    T = ids.numel()
+    if positions.numel() != T or freq.numel() != (W + 1) // 2:
+        raise KernelError("embed_sinusoid: one position per token and one frequency per pair")
+    out = torch.empty((T, W), dtype=torch.float32, device=table.device)
+    _check(_lib().ix_embed_sinusoid(_ptr(table), _dtype_code(table), _ptr(ids), _ptr(positions),
+                                    _ptr(freq), T, W, V, _ptr(out), ctypes.c_float(scale),
+                                    _stream()), "embed_sinusoid")
+    _count()
+    return out
+
+
+def add_rmsnorm_sum(resid: torch.Tensor, terms, vector: Optional[torch.Tensor], gains,
+                    eps: float, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None):
+    """resid += sum(terms) + vector (kept when ``rows`` is None), then one normed view of the
+    rows per gain: RMSNorm(resid) * gain.  ``terms``: up to three tensors shaped like
+    ``resid``, each fp32 or bfloat16 (one that is still unwritten is written out first);
+    ``vector``: fp32 [width] added to every row, or None; ``gains``: one or two fp32 [width].
+    With ``rows`` the listed rows are gathered and the residual is left as it was."""
+    _chk("resid", resid, torch.float32)
+    _chk("vector", vector, torch.float32, optional=True)
+    _chk("rows", rows, torch.int32, optional=True)
+    T, W = resid.shape
+    terms = [t.materialize() if hasattr(t, "materialize") else t for t in terms]
+    while len(terms) > 3:                      # more than the kernel adds at once
+        terms = [terms[0].to(torch.float32) + terms[1].to(torch.float32)] + terms[2:]
+    for i, t in enumerate(terms):
+        _chk(f"terms[{i}]", t)
+        if t.shape != resid.shape:
+            raise KernelError(f"add_rmsnorm_sum: term {i} is {tuple(t.shape)}, the residual "
+                              f"{tuple(resid.shape)}")
+    if not 1 <= len(gains) <= 2:
+        raise KernelError("add_rmsnorm_sum: one or two gains")
+    for g in gains:
+        _chk("gain", g, torch.float32)
+        if g.numel() != W:
+            raise KernelError(f"add_rmsnorm_sum: gain has {g.numel()} entries, rows have {W}")
+    if vector is not None and vector.numel() != W:
+        raise KernelError("add_rmsnorm_sum: the vector must have the residual's width")
+    R = T if rows is None else rows.numel()
+    outs = [torch.empty((R, W), dtype=out_dtype, device=resid.device) for _ in gains]
+    d = terms + [None] * (3 - len(terms))
+    codes = [_dtype_code(t) if t is not None else 0 for t in d]
+    _check(_lib().ix_add_rmsnorm_sum(
+        _ptr(resid), _ptr(d[0]), codes[0], _ptr(d[1]), codes[1], _ptr(d[2]), codes[2],
+        _ptr(vector), _ptr(rows), _ptr(gains[0]), _ptr(gains[1] if len(gains) > 1 else None),
+        _ptr(outs[0]), _ptr(outs[1] if len(outs) > 1 else None), _dtype_code(outs[0]), R, W,
+        ctypes.c_float(eps), 1 if rows is None else 0, _stream()), "add_rmsnorm_sum")
+    _count()
+    return tuple(outs)
+
+
+def qk_norm_append(qk: torch.Tensor, q_gain: torch.Tensor, k_gain: torch.Tensor,
+                   positions: torch.Tensor, heads: int, kv_heads: int, head_dim: int, eps: float,
+                   temp_coef: float, temp_every: int, k_cache: Optional[torch.Tensor],
+                   v_cache: Optional[torch.Tensor], slots: Optional[torch.Tensor]):
+    """``qk`` [T, (heads + kv_heads) * head_dim] holds q then k.  Returns q [T, heads, hd],
+    RMS-normed per head with ``q_gain`` and multiplied by 1 + temp_coef * ln(floor((p + 1)
+    / temp_every) + 1) (``temp_every`` 0: by 1); writes k RMS-normed with ``k_gain`` into
+    ``k_cache`` and k as it is into ``v_cache`` at ``slots`` when caches are given."""
+    _chk("qk", qk)
+    _chk("q_gain", q_gain, torch.float32)
+    _chk("k_gain", k_gain, torch.float32)
+    _chk("positions", positions, torch.int32)
+    _chk("k_cache", k_cache, qk.dtype, optional=True)
+    _chk("v_cache", v_cache, qk.dtype, optional=True)
+    _chk("slots", slots, torch.int32, optional=True)
+    T = qk.shape[0]
+    if qk.shape[1] != (heads + kv_heads) * head_dim or q_gain.numel() != head_dim \
+            or k_gain.numel() != head_dim:
+        raise KernelError("qk_norm_append: sizes of the projection or the gains do not fit")
+    page = 1
+    if k_cache is not None:
+        if v_cache is None or v_cache.shape != k_cache.shape or k_cache.shape[1] != kv_heads \
+                or k_cache.shape[3] != head_dim or slots is None or slots.numel() != T:
+            raise KernelError("qk_norm_append: cache geometry differs from the projection's")
+        page = k_cache.shape[2]
+    q = torch.empty((T, heads, head_dim), dtype=qk.dtype, device=qk.device)
+    _check(_lib().ix_qk_norm_append(
+        _ptr(qk), _dtype_code(qk), _ptr(q_gain), _ptr(k_gain), _ptr(positions), _ptr(q),
+        _ptr(k_cache), _ptr(v_cache), _ptr(slots), T, heads, kv_heads, head_dim, page,
+        ctypes.c_float(eps), ctypes.c_float(temp_coef), int(temp_every), _stream()),
+        "qk_norm_append")
+    _count()
+    return q
+
+
+def _row_view(name: str, t: torch.Tensor, width: int) -> int:
+    """The row stride of a 2-d view with unit inner stride (a slice of columns of a
+    projection's output, for instance)."""
+    if not isinstance(t, torch.Tensor) or not t.is_cuda or t.dim() != 2 or t.shape[1] != width \
+            or (width > 1 and t.stride(1) != 1):
+        raise KernelError(f"{name}: expected a CUDA view [rows, {width}] with unit inner stride")
+    return max(int(t.stride(0)), width)
+
+
+def shift_mix(x: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, step):
+    """out[m, t] = x[t] + (x[t-1] - x[t]) * mu[m], computed in fp32, in x's element type.
+    The row before a sequence's first token of this step comes from
+    ``state[state_slot[s]]`` ([slots, width] fp32), which then takes the sequence's last
+    row of this step."""
+    _chk("x", x)
+    _chk("mu", mu, torch.float32)
+    _chk("state", state, torch.float32)
+    T, W = x.shape
+    if mu.dim() != 2 or mu.shape[1] != W or state.shape[1] != W:
+        raise KernelError("shift_mix: mu and state must have the input's width")
+    out = torch.empty((mu.shape[0], T, W), dtype=x.dtype, device=x.device)
+    _check(_lib().ix_shift_mix(_ptr(x), _dtype_code(x), _ptr(mu), _ptr(state), _ptr(step.cu_q),
+                               _ptr(step.seq_of_token), _ptr(step.state_slot), _ptr(out), T, W,
+                               mu.shape[0], _stream()), "shift_mix")
+    _count()
+    return out
+
+
+_DECAY_FORMS = {"exp_exp_tanh": 0, "sigmoid_root": 1}
+
+
+def lowrank_decay(x: torch.Tensor, w2: torch.Tensor, b: Optional[torch.Tensor], mode: str,
+                  tau: float = 1.0):
+    """fp32 [T, C] decays from the inner activations ``x`` [T, R] of a low-rank product
+    (a view with unit inner stride): z = act(x) . w2^T + b with w2 fp32 [C, R], then
+    "exp_exp_tanh": exp(-exp(z)) with act = tanh; "sigmoid_root": sigmoid(z)^(1/tau) with
+    act the identity."""
+    _chk("w2", w2, torch.float32)
+    _chk("b", b, torch.float32, optional=True)
+    if mode not in _DECAY_FORMS:
+        raise KernelError(f"lowrank_decay: unknown form {mode!r}; known: {sorted(_DECAY_FORMS)}")
+    C, R = w2.shape
+    ldx = _row_view("lowrank_decay: x", x, R)
+    T = x.shape[0]
+    out = torch.empty((T, C), dtype=torch.float32, device=x.device)
+    _check(_lib().ix_lowrank_decay(_ptr(x), _dtype_code(x), ctypes.c_longlong(ldx), _ptr(w2),
+                                   _ptr(b), _ptr(out), T, C, R, _DECAY_FORMS[mode],
+                                   ctypes.c_float(tau), _stream()), "lowrank_decay")
+    _count()
+    return out
+
+
+def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor,
+                      bonus: Optional[torch.Tensor], state: torch.Tensor, step, heads: int,
+                      dim: int, vdim: int, q_scale: float = 1.0, bonus_form: bool = False):
+    """Walks every sequence's tokens of this step in order, per head with a state
+    S [dim, vdim] in ``state[state_slot[s]]`` ([slots, heads, dim, vdim] fp32, updated):
+    plain form S = diag(w_t) S + k_t v_t^T, o_t = S^T q_t; bonus form o_t = (S + diag(u)
+    k_t v_t^T)^T q_t, then S = diag(w_t) S + k_t v_t^T.  q, k [T, heads * dim] and
+    v [T, heads * vdim] are views with unit inner stride, ``decay`` fp32 [T, heads * dim],
+    ``bonus`` fp32 [heads, dim].  Returns fp32 [T, heads, vdim]."""
+    ldq = _row_view("linear_recurrence: q", q, heads * dim)
+    ldk = _row_view("linear_recurrence: k", k, heads * dim)
+    ldv = _row_view("linear_recurrence: v", v, heads * vdim)
+    _chk("decay", decay, torch.float32)
+    _chk("bonus", bonus, torch.float32, optional=True)
+    _chk("state", state, torch.float32)
+    T = q.shape[0]
+    if not (q.dtype == k.dtype == v.dtype) or k.shape[0] != T or v.shape[0] != T \
+            or decay.shape != (T, heads * dim) or tuple(state.shape[1:]) != (heads, dim, vdim):
+        raise KernelError("linear_recurrence: q, k, v, decay and state do not fit together")
+    if bonus_form and (bonus is None or bonus.numel() != heads * dim):
+        raise KernelError("linear_recurrence: the bonus form needs u [heads, dim]")
+    out = torch.empty((T, heads, vdim), dtype=torch.float32, device=q.device)
+    _check(_lib().ix_linear_recurrence(
+        _ptr(q), ctypes.c_longlong(ldq), _ptr(k), ctypes.c_longlong(ldk), _ptr(v),
+        ctypes.c_longlong(ldv), _dtype_code(q), _ptr(decay), _ptr(bonus), _ptr(state),
+        _ptr(step.cu_q), _ptr(step.state_slot), _ptr(out), step.num_seqs, heads, dim, vdim,
+        ctypes.c_float(q_scale), 1 if bonus_form else 0, _stream()), "linear_recurrence")
+    _count()
+    return out
+
+
+def check_recurrence_limits(dim: int, where: str = ""):
+    most = _lib().ix_linear_recurrence_max_dim()
+    if dim > most:
+        raise KernelError(f"{where}: {dim} key entries per head exceed the recurrence "
+                          f"kernel's {most}")
+
+
+def head_norm_gate(o: torch.Tensor, gain: torch.Tensor, gate: torch.Tensor, eps: float,
+                   out_dtype: torch.dtype):
+    """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * gain * silu(gate[t, h]) for
+    o fp32 [T, heads, vdim]; ``gain`` fp32 [vdim] (shared by the heads) or [heads * vdim];
+    ``gate`` a view [T, heads * vdim] with unit inner stride in ``out_dtype``."""
+    _chk("o", o, torch.float32)
+    _chk("gain", gain, torch.float32)
+    T, H, V = o.shape
+    ldg = _row_view("head_norm_gate: gate", gate, H * V)
+    if gain.numel() not in (V, H * V) or gate.dtype != out_dtype or gate.shape[0] != T:
+        raise KernelError("head_norm_gate: gain or gate do not fit the heads")
+    out = torch.empty((T, H * V), dtype=out_dtype, device=o.device)
+    _check(_lib().ix_head_norm_gate(
+        _ptr(o), _ptr(gain), 1 if (gain.numel() == H * V and H > 1) else 0, _ptr(gate),
+        _dtype_code(gate), ctypes.c_longlong(ldg), _ptr(out), _dtype_code(out), T, H, V,
+        ctypes.c_float(eps), _stream()), "head_norm_gate")
     _count()
     return out

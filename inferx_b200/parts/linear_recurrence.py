@@ -37,6 +37,11 @@ class GatedLinearAttention:
         self.spec, self.ctx, self.p = spec, ctx, prefix
         self.front_w = self.a2_w = self.a2_b = self.norm_w = self.o_w = None
 
+    def check_limits(self):
+        check = getattr(self.ctx.ops, "check_recurrence_limits", None)
+        if check is not None:
+            check(self.spec.dim, self.p)
+
     def tensors(self):
         s, p = self.spec, self.p
         hk, hv, r = s.heads * s.dim, s.heads * s.vdim, _rank(s.decay_rank)
@@ -84,6 +89,11 @@ class GatedLinearAttention:
 class WkvMixer:
     def __init__(self, spec, ctx, prefix: str):
         self.spec, self.ctx, self.p = spec, ctx, prefix
+
+    def check_limits(self):
+        check = getattr(self.ctx.ops, "check_recurrence_limits", None)
+        if check is not None:
+            check(self.spec.dim, self.p)
 
     def tensors(self):
         s, p = self.spec, self.p
