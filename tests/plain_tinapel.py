@@ -10,11 +10,45 @@ Notation: ``h`` is a mixer's or feed-forward's input (a normed row of the stream
 """
 from __future__ import annotations
 
+import json
 import math
+import os
 
 import torch
 
 F = torch.float64
+
+
+def read_model_folder(path):
+    from inferx_b200.weights.safetensors_io import Checkpoint
+    with open(os.path.join(path, "config.json")) as f:
+        cfg = json.load(f)
+    ck = Checkpoint(path)
+    w = {n: ck.get(n).clone() for n in ck.names()}
+    ck.close()
+    return cfg, w
+
+
+def same(t):
+    return t
+
+
+def round_bf16(t):
+    return t.to(torch.float32).to(torch.bfloat16).to(t.dtype)
+
+
+def round_f32(t):
+    return t.to(torch.float32).to(t.dtype)
+
+
+# What a run in a narrower element type stores between its kernels passes through
+# ``_store`` (the identity for the exact model; ``forward(..., store=round_bf16)`` imitates
+# a bfloat16 run to measure what its rounding alone costs).
+_store = same
+
+
+def st(t):
+    return _store(t)
 
 
 def rms(x, eps):
@@ -24,10 +58,6 @@ def rms(x, eps):
 
 def norm_one_plus(x, w, eps):
     return rms(x, eps) * (1.0 + w)
-
-
-def gelu_tanh(z):
-    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
 
 
 def silu(z):
@@ -59,10 +89,10 @@ def gla_mixer(w, p, m, h, eps):
     H, K = m["heads"], m["dim"]
     V = m.get("vdim", K)
     g = lambda n: w[f"{p}.{n}"].to(F)
-    q = (h @ g("q").T).view(T, H, K) * K ** -0.5
-    k = (h @ g("k").T).view(T, H, K)
-    v = (h @ g("v").T).view(T, H, V)
-    z = (h @ g("a1").T) @ g("a2").T + g("a2.b")
+    q = st(h @ g("q").T).view(T, H, K) * K ** -0.5
+    k = st(h @ g("k").T).view(T, H, K)
+    v = st(h @ g("v").T).view(T, H, V)
+    z = st(h @ g("a1").T) @ g("a2").T + g("a2.b")
     a = torch.sigmoid(z).pow(1.0 / m["tau"]).view(T, H, K)
     S = torch.zeros(H, K, V, dtype=F)
     o = torch.zeros(T, H, V, dtype=F)
@@ -70,7 +100,7 @@ def gla_mixer(w, p, m, h, eps):
         S = a[t][:, :, None] * S + k[t][:, :, None] * v[t][:, None, :]
         o[t] = torch.einsum("hkv,hk->hv", S, q[t])
     o = rms(o, eps) * g("norm")
-    return (o.reshape(T, H * V) * silu(h @ g("g").T)) @ g("o").T
+    return st(o.reshape(T, H * V) * silu(st(h @ g("g").T))) @ g("o").T
 
 
 def attention_mixer(w, p, m, h, eps):
@@ -80,15 +110,16 @@ def attention_mixer(w, p, m, h, eps):
     T = h.shape[0]
     H, G, D = m["heads"], m["kv_heads"], m["dim"]
     g = lambda n: w[f"{p}.{n}"].to(F)
-    q = (h @ g("q").T).view(T, H, D)
-    k_raw = (h @ g("k").T).view(T, G, D)
+    q = st(h @ g("q").T).view(T, H, D)
+    k_raw = st(h @ g("k").T).view(T, G, D)
     v = k_raw
     q = rms(q, eps) * g("q.norm")
-    k = rms(k_raw, eps) * g("k.norm")
+    k = st(rms(k_raw, eps) * g("k.norm"))
     qt = m.get("q_temp")
     if qt:
         pos = torch.arange(T, dtype=F)
         q = q * (1.0 + qt["coef"] * torch.log(torch.floor((pos + 1) / qt["every"]) + 1.0))[:, None, None]
+    q = st(q)
     out = torch.zeros(T, H, D, dtype=F)
     cap = m.get("softcap")
     for hh in range(H):
@@ -98,7 +129,7 @@ def attention_mixer(w, p, m, h, eps):
             s = cap * torch.tanh(s / cap)
         s = s.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), -math.inf)
         out[:, hh] = torch.softmax(s, -1) @ v[:, kv]
-    return out.reshape(T, H * D) @ g("o").T
+    return st(out.reshape(T, H * D)) @ g("o").T
 
 
 def wkv_mixer(w, p, m, h, eps):
@@ -108,11 +139,11 @@ def wkv_mixer(w, p, m, h, eps):
     H, K = m["heads"], m["dim"]
     g = lambda n: w[f"{p}.{n}"].to(F)
     prev = torch.cat([torch.zeros(1, h.shape[1], dtype=F), h[:-1]], 0)
-    mix = lambda s: h + (prev - h) * g(f"mu.{s}")
-    r = (mix("r") @ g("r").T).view(T, H, K)
-    k = (mix("k") @ g("k").T).view(T, H, K)
-    v = (mix("v") @ g("v").T).view(T, H, K)
-    gate = silu(mix("g") @ g("g").T)
+    mix = lambda s: st(h + (prev - h) * g(f"mu.{s}"))
+    r = st(mix("r") @ g("r").T).view(T, H, K)
+    k = st(mix("k") @ g("k").T).view(T, H, K)
+    v = st(mix("v") @ g("v").T).view(T, H, K)
+    gate = silu(st(mix("g") @ g("g").T))
     dec = torch.exp(-torch.exp(torch.tanh(mix("w") @ g("w1").T) @ g("w2").T + g("w0"))).view(T, H, K)
     u = g("u").view(H, K)
     S = torch.zeros(H, K, K, dtype=F)
@@ -122,7 +153,7 @@ def wkv_mixer(w, p, m, h, eps):
         o[t] = torch.einsum("hkv,hk->hv", S + u[:, :, None] * kv, r[t])
         S = dec[t][:, :, None] * S + kv
     o = rms(o, eps).reshape(T, H * K) * g("norm")
-    return (o * gate) @ g("o").T
+    return st(o * gate) @ g("o").T
 
 
 MIXERS = {"gla": gla_mixer, "attention": attention_mixer, "wkv": wkv_mixer}
@@ -131,7 +162,7 @@ MIXERS = {"gla": gla_mixer, "attention": attention_mixer, "wkv": wkv_mixer}
 # ---------------------------------------------------------------------------------------
 def expert(w, p, h):
     g = lambda n: w[f"{p}.{n}"].to(F)
-    return (silu(h @ g("gate").T) * (h @ g("up").T)) @ g("down").T
+    return st(st(silu(h @ g("gate").T) * (h @ g("up").T)) @ g("down").T)
 
 
 def route(w, p, mlp, h):
@@ -150,15 +181,16 @@ def moe(w, p, mlp, h):
             out[t] += c * expert(w, f"{p}.e{e}", h[t:t + 1])[0]
     if mlp.get("shared"):
         out = out + expert(w, f"{p}.shared", h)
-    return out
+    return st(out)
 
 
 # ---------------------------------------------------------------------------------------
 def layer(w, cfg, i, x):
     lc, eps = cfg["layers"][i], cfg["norm"]["eps"]
-    d = MIXERS[lc["type"]](w, f"l{i}.mix", lc["mixer"], norm_one_plus(x, w[f"l{i}.norm1"].to(F), eps), eps)
+    d = MIXERS[lc["type"]](w, f"l{i}.mix", lc["mixer"],
+                           st(norm_one_plus(x, w[f"l{i}.norm1"].to(F), eps)), eps)
     if lc.get("mlp") is not None:
-        d = d + moe(w, f"l{i}.mlp", lc["mlp"], norm_one_plus(x, w[f"l{i}.norm2"].to(F), eps))
+        d = d + moe(w, f"l{i}.mlp", lc["mlp"], st(norm_one_plus(x, w[f"l{i}.norm2"].to(F), eps)))
     return x + d
 
 
@@ -176,7 +208,16 @@ def layer_runs(cfg):
     return runs + [(i, None) for i in range(b, n)]
 
 
-def forward(w, cfg, tokens, want_stream=False):
+def forward(w, cfg, tokens, want_stream=False, store=same):
+    global _store
+    _store = store
+    try:
+        return _forward(w, cfg, tokens, want_stream)
+    finally:
+        _store = same
+
+
+def _forward(w, cfg, tokens, want_stream):
     x0 = embedding(w, cfg, tokens)
     x = x0.clone()
     stream = []
@@ -187,6 +228,6 @@ def forward(w, cfg, tokens, want_stream=False):
             x = x + w["loop.step"].to(F)[t]
         x = layer(w, cfg, i, x)
         stream.append(x.clone())
-    n = norm_one_plus(x, w["final.norm"].to(F), cfg["norm"]["eps"])
+    n = st(norm_one_plus(x, w["final.norm"].to(F), cfg["norm"]["eps"]))
     logits = n @ w["embed"].to(F).T
     return (logits, torch.stack(stream)) if want_stream else logits
