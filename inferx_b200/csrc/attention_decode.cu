@@ -679,12 +679,36 @@ extern "C" int ix_attn_decode_tma_partials(const void* q, const void* kc, const 
                                            int window, float scale, int splits, int* status,
                                            cudaStream_t stream);
 
+extern "C" int ix_attn_decode_tma_partials_capped(
+    const void* q, const void* kc, const void* vc, int num_pages, const int* bt,
+    const int* kv_len, float* part_o, float* part_ml, void* out, int S, int heads, int kvh,
+    int hd, int page_size, int maxb, int window, float scale, float softcap, int splits,
+    int* status, cudaStream_t stream);
+
+IX_API int ix_paged_attention_decode_tma_capped(
+    const void* q, const void* k_cache, const void* v_cache, int num_pages,
+    const int* block_table, const int* kv_len, float* part_o, float* part_ml, void* out, int S,
+    int heads, int kvh, int hd, int page_size, int max_blocks, int window, float scale,
+    float softcap, int splits, int* status, cudaStream_t stream);
+
 IX_API int ix_paged_attention_decode_tma(const void* q, const void* k_cache, const void* v_cache,
                                          int num_pages, const int* block_table,
                                          const int* kv_len, float* part_o, float* part_ml,
                                          void* out, int S, int heads, int kvh, int hd,
                                          int page_size, int max_blocks, int window, float scale,
                                          int splits, int* status, cudaStream_t stream) {
+  return ix_paged_attention_decode_tma_capped(q, k_cache, v_cache, num_pages, block_table, kv_len,
+                                              part_o, part_ml, out, S, heads, kvh, hd, page_size,
+                                              max_blocks, window, scale, 0.f, splits, status,
+                                              stream);
+}
+
+// The same with scores squashed to softcap * tanh(score / softcap) when softcap > 0.
+IX_API int ix_paged_attention_decode_tma_capped(
+    const void* q, const void* k_cache, const void* v_cache, int num_pages,
+    const int* block_table, const int* kv_len, float* part_o, float* part_ml, void* out, int S,
+    int heads, int kvh, int hd, int page_size, int max_blocks, int window, float scale,
+    float softcap, int splits, int* status, cudaStream_t stream) {
   if (S <= 0) return IX_OK;
   if (heads <= 0 || kvh <= 0 || heads % kvh != 0 || max_blocks <= 0 || window < 0 || splits < 1)
     return IX_ERR_SIZE;
@@ -692,9 +716,10 @@ IX_API int ix_paged_attention_decode_tma(const void* q, const void* k_cache, con
   if (splits > 1 && (part_o == nullptr || part_ml == nullptr)) return IX_ERR_SIZE;
   if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) return IX_ERR_ALIGN;
   if (!ix_attn_decode_tma_applies(hd, page_size)) return IX_ERR_UNSUPPORTED;
-  int rc = ix_attn_decode_tma_partials(q, k_cache, v_cache, num_pages, block_table, kv_len, part_o,
-                                       part_ml, out, S, heads, kvh, hd, page_size, max_blocks,
-                                       window, scale, splits, status, stream);
+  int rc = ix_attn_decode_tma_partials_capped(q, k_cache, v_cache, num_pages, block_table, kv_len,
+                                              part_o, part_ml, out, S, heads, kvh, hd, page_size,
+                                              max_blocks, window, scale, softcap, splits, status,
+                                              stream);
   if (rc != 0 || splits == 1) return rc;
   ix_launch(attn_decode_merge_kernel<bf16, true>, dim3(S * heads), dim3(hd >= 128 ? 128 : 64), 0,
             stream, (const float*)part_o, (const float*)part_ml, (bf16*)out, hd, splits);

@@ -80,7 +80,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                        float* __restrict__ part_o, float* __restrict__ part_ml,
                        bf16* __restrict__ out, int heads, int kvh, int page_size, int page_shift,
                        int maxb, int window, float scale_log2e, int splits,
-                       int* __restrict__ status) {
+                       int* __restrict__ status, float cap_c1, float cap_over_scale) {
   constexpr int CH = HD / 8, KS = HD / 16, DTL = HD / 8, HALVES = HD / 64;
   constexpr int TILE_BYTES = DT_BN * HD * 2;
   extern __shared__ unsigned char dsm_raw[];
@@ -248,7 +248,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             const int kp = kw + j * 8 + 2 * t + (c & 1);
-            const float v = (kp < k1 && kp >= lo) ? sc[j][c] * scale_log2e : -INFINITY;
+            const float raw = cap_over_scale > 0.f
+                                  ? ix_cap_raw_score(sc[j][c], cap_c1, cap_over_scale)
+                                  : sc[j][c];
+            const float v = (kp < k1 && kp >= lo) ? raw * scale_log2e : -INFINITY;
             sc[j][c] = v;
             mx[c >> 1] = fmaxf(mx[c >> 1], v);
           }
@@ -359,7 +362,8 @@ template <int HD>
 static int launch_tma(const void* q, const void* kc, const void* vc, long long cache_rows,
                       const int* bt, const int* kv_len, float* part_o, float* part_ml, void* out,
                       int S, int heads, int kvh, int page_size, int page_shift, int maxb,
-                      int window, float scale, int splits, int* status, cudaStream_t stream) {
+                      int window, float scale, float softcap, int splits, int* status,
+                      cudaStream_t stream) {
   CUtensorMap map_k, map_v;
   int rc = ix_tensor_map_bf16_2d(&map_k, kc, cache_rows, HD, 64, page_size);
   if (rc != IX_OK) return rc;
@@ -374,7 +378,8 @@ static int launch_tma(const void* q, const void* kc, const void* vc, long long c
   if (e != cudaSuccess) return (int)e;
   ix_launch(kern, grid, dim3(DT_THREADS), smem, stream, map_k, map_v, (const bf16*)q, bt, kv_len,
             part_o, part_ml, (bf16*)out, heads, kvh, page_size, page_shift, maxb, window, sl2,
-            splits, status);
+            splits, status, softcap > 0.f ? 2.f * sl2 / softcap : 0.f,
+            softcap > 0.f ? softcap / scale : 0.f);
   return ix_launch_status();
 }
 
@@ -387,12 +392,30 @@ extern "C" int ix_attn_decode_tma_applies(int hd, int page_size) {
 // The split pass alone (partials into part_o / part_ml, or `out` when splits == 1);
 // the caller launches the merge.  num_pages: pages in the cache tensors; status: one
 // int in device memory, zero before the first call.
+extern "C" int ix_attn_decode_tma_partials_capped(
+    const void* q, const void* kc, const void* vc, int num_pages, const int* bt,
+    const int* kv_len, float* part_o, float* part_ml, void* out, int S, int heads, int kvh,
+    int hd, int page_size, int maxb, int window, float scale, float softcap, int splits,
+    int* status, cudaStream_t stream);
+
 extern "C" int ix_attn_decode_tma_partials(const void* q, const void* kc, const void* vc,
                                            int num_pages, const int* bt, const int* kv_len,
                                            float* part_o, float* part_ml, void* out, int S,
                                            int heads, int kvh, int hd, int page_size, int maxb,
                                            int window, float scale, int splits, int* status,
                                            cudaStream_t stream) {
+  return ix_attn_decode_tma_partials_capped(q, kc, vc, num_pages, bt, kv_len, part_o, part_ml, out,
+                                            S, heads, kvh, hd, page_size, maxb, window, scale, 0.f,
+                                            splits, status, stream);
+}
+
+// softcap > 0: scores squashed to softcap * tanh(score / softcap); 0: as they are.
+extern "C" int ix_attn_decode_tma_partials_capped(
+    const void* q, const void* kc, const void* vc, int num_pages, const int* bt,
+    const int* kv_len, float* part_o, float* part_ml, void* out, int S, int heads, int kvh,
+    int hd, int page_size, int maxb, int window, float scale, float softcap, int splits,
+    int* status, cudaStream_t stream) {
+  if (softcap < 0.f || (softcap > 0.f && !(scale > 0.f))) return IX_ERR_SIZE;
   if (!ix_attn_decode_tma_applies(hd, page_size) || num_pages <= 0) return IX_ERR_UNSUPPORTED;
   if (status == nullptr) return IX_ERR_SIZE;
   int page_shift = 0;
@@ -401,7 +424,9 @@ extern "C" int ix_attn_decode_tma_partials(const void* q, const void* kc, const 
   if (cache_rows > 0x7fffffffLL) return IX_ERR_SIZE;
   if (hd == 128)
     return launch_tma<128>(q, kc, vc, cache_rows, bt, kv_len, part_o, part_ml, out, S, heads, kvh,
-                           page_size, page_shift, maxb, window, scale, splits, status, stream);
+                           page_size, page_shift, maxb, window, scale, softcap, splits, status,
+                           stream);
   return launch_tma<64>(q, kc, vc, cache_rows, bt, kv_len, part_o, part_ml, out, S, heads, kvh,
-                        page_size, page_shift, maxb, window, scale, splits, status, stream);
+                        page_size, page_shift, maxb, window, scale, softcap, splits, status,
+                        stream);
 }

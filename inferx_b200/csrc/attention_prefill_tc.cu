@@ -96,7 +96,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                        const int* __restrict__ q_pos0, bf16* __restrict__ out, int S, int heads,
                        int kvh, int page_size, int page_shift, int maxb, int window,
                        float scale_log2e, int* __restrict__ status, int nsplit,
-                       float* __restrict__ part_o, float* __restrict__ part_ml) {
+                       float* __restrict__ part_o, float* __restrict__ part_ml, float cap_c1,
+                       float cap_over_scale) {
   constexpr int HALVES = HD / 64;
   constexpr int Q_BYTES = FA_BM * HD * 2;
   constexpr int Q_HALF = FA_BM * 128;
@@ -299,6 +300,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       float sc[FA_BN];
       tc_ld32(lane_addr + S_COL + st * FA_BN, sc);
       tc_ld32(lane_addr + S_COL + st * FA_BN + 32, sc + 32);
+      if (cap_over_scale > 0.f) {       // squashed scores: everything below sees them as raw
+#pragma unroll
+        for (int i = 0; i < FA_BN; ++i) sc[i] = ix_cap_raw_score(sc[i], cap_c1, cap_over_scale);
+      }
       const int kbase = kt0 + j * FA_BN;
       const bool need_mask = (kbase + FA_BN - 1 > pos0) || kbase < kv_lo ||
                              (window > 0 && kbase < pmax - window + 1);
@@ -465,8 +470,8 @@ template <int HD>
 static int launch_prefill_tc(const void* q, const void* kc, const void* vc, long long cache_rows,
                              const int* bt, const int* cu_q, const int* q_pos0, void* out, int T,
                              int S, int heads, int kvh, int page_size, int page_shift, int maxb,
-                             int window, float scale, int* status, int nsplit, float* part_o,
-                             float* part_ml, cudaStream_t stream) {
+                             int window, float scale, float softcap, int* status, int nsplit,
+                             float* part_o, float* part_ml, cudaStream_t stream) {
   CUtensorMap map_q, map_k, map_v;
   int rc = ix_tensor_map_bf16_2d(&map_q, q, T, (long long)heads * HD, 64, FA_BM);
   if (rc != IX_OK) return rc;
@@ -484,7 +489,10 @@ static int launch_prefill_tc(const void* q, const void* kc, const void* vc, long
   kern<<<grid, FA_THREADS, smem, stream>>>(map_q, map_k, map_v, bt, cu_q, q_pos0, (bf16*)out, S,
                                            heads, kvh, page_size, page_shift, maxb, window,
                                            scale * 1.4426950408889634f, status, nsplit, part_o,
-                                           part_ml);
+                                           part_ml,
+                                           softcap > 0.f ? 2.f * scale * 1.4426950408889634f / softcap
+                                                         : 0.f,
+                                           softcap > 0.f ? softcap / scale : 0.f);
   rc = ix_launch_status();
   if (rc != IX_OK || nsplit == 1) return rc;
   attn_prefill_tc_merge_kernel<<<T * heads, HD >= 128 ? 128 : 64, 0, stream>>>(
@@ -513,12 +521,43 @@ IX_API int ix_attn_prefill_tc_splits(int T, int S, int heads, int keys, int wind
 // q: [T, heads, hd] bf16; caches [num_pages, kvh, page_size, hd] bf16; status: one int
 // in device memory, zero before the first call.  splits > 1: part_o [T, heads, splits,
 // hd] and part_ml [T, heads, splits, 2] fp32 scratch.
+static int prefill_tc_checked(const void* q, const void* k_cache, const void* v_cache,
+                              int num_pages, const int* block_table, const int* cu_q,
+                              const int* q_pos0, void* out, int T, int S, int heads, int kvh,
+                              int hd, int page_size, int max_blocks, int window, float scale,
+                              float softcap, int splits, float* part_o, float* part_ml,
+                              int* status, cudaStream_t stream);
+
 IX_API int ix_paged_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache,
                                          int num_pages, const int* block_table, const int* cu_q,
                                          const int* q_pos0, void* out, int T, int S, int heads,
                                          int kvh, int hd, int page_size, int max_blocks,
                                          int window, float scale, int splits, float* part_o,
                                          float* part_ml, int* status, cudaStream_t stream) {
+  return prefill_tc_checked(q, k_cache, v_cache, num_pages, block_table, cu_q, q_pos0, out, T, S,
+                            heads, kvh, hd, page_size, max_blocks, window, scale, 0.f, splits,
+                            part_o, part_ml, status, stream);
+}
+
+// The same with scores squashed to softcap * tanh(score / softcap) (softcap > 0 and a
+// positive scale).
+IX_API int ix_paged_attention_prefill_tc_capped(
+    const void* q, const void* k_cache, const void* v_cache, int num_pages,
+    const int* block_table, const int* cu_q, const int* q_pos0, void* out, int T, int S,
+    int heads, int kvh, int hd, int page_size, int max_blocks, int window, float scale,
+    float softcap, int splits, float* part_o, float* part_ml, int* status, cudaStream_t stream) {
+  if (!(softcap > 0.f) || !(scale > 0.f)) return IX_ERR_SIZE;
+  return prefill_tc_checked(q, k_cache, v_cache, num_pages, block_table, cu_q, q_pos0, out, T, S,
+                            heads, kvh, hd, page_size, max_blocks, window, scale, softcap, splits,
+                            part_o, part_ml, status, stream);
+}
+
+static int prefill_tc_checked(const void* q, const void* k_cache, const void* v_cache,
+                              int num_pages, const int* block_table, const int* cu_q,
+                              const int* q_pos0, void* out, int T, int S, int heads, int kvh,
+                              int hd, int page_size, int max_blocks, int window, float scale,
+                              float softcap, int splits, float* part_o, float* part_ml,
+                              int* status, cudaStream_t stream) {
   if (T <= 0 || S <= 0) return IX_OK;
   if (heads <= 0 || kvh <= 0 || heads % kvh != 0 || max_blocks <= 0 || window < 0 ||
       num_pages <= 0 || status == nullptr)
@@ -538,8 +577,8 @@ IX_API int ix_paged_attention_prefill_tc(const void* q, const void* k_cache, con
   if (hd == 128)
     return launch_prefill_tc<128>(q, k_cache, v_cache, cache_rows, block_table, cu_q, q_pos0, out,
                                   T, S, heads, kvh, page_size, page_shift, max_blocks, window,
-                                  scale, status, splits, part_o, part_ml, stream);
+                                  scale, softcap, status, splits, part_o, part_ml, stream);
   return launch_prefill_tc<64>(q, k_cache, v_cache, cache_rows, block_table, cu_q, q_pos0, out, T,
                                S, heads, kvh, page_size, page_shift, max_blocks, window, scale,
-                               status, splits, part_o, part_ml, stream);
+                               softcap, status, splits, part_o, part_ml, stream);
 }

@@ -62,6 +62,16 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return total;
 }
 
+// Scores squashed by tanh, on the raw score: for a raw score s (before the scale) returns
+// the raw score whose scaled value is cap * tanh(s * scale / cap).  c1 = 2 * scale *
+// log2(e) / cap and cap_over_scale = cap / scale; tanh(y) = 1 - 2 / (exp(2y) + 1) with the
+// fast exp2 and division (an error of some 1e-7 of the cap on the scaled score).
+__device__ __forceinline__ float ix_cap_raw_score(float s, float c1, float cap_over_scale) {
+  float t;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fminf(s * c1, 80.f)));
+  return cap_over_scale * (1.f - __fdividef(2.f, t + 1.f));
+}
+
 // ---------------------------------------------------------------------------
 // Programmatic dependent launch.  A kernel that starts with IX_PDL_WAIT() may be
 // launched with ix_launch(): it is then allowed onto the SMs while its predecessor

@@ -620,7 +620,8 @@ def _tma_decode_applies(q, page: int) -> bool:
 def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                            block_table: torch.Tensor, kv_len: torch.Tensor, max_kv_len: int,
                            window: int, scale: float, splits: Optional[int] = None,
-                           kernel: Optional[str] = None, out: Optional[torch.Tensor] = None):
+                           kernel: Optional[str] = None, out: Optional[torch.Tensor] = None,
+                           softcap: float = 0.0):
     """Split-KV attention for a batch in which sequence s brings the one query q[s]
     at position kv_len[s] - 1.  ``kernel`` picks a form ("tma", "mma", "scalar");
     None takes the fastest that applies."""
@@ -645,6 +646,8 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
             kernel = "mma"
     if kernel not in ("tma", "mma", "scalar"):
         raise KernelError(f"paged_attention_decode: no kernel form {kernel!r}")
+    if softcap > 0 and kernel != "tma":
+        raise KernelError("paged_attention_decode: only the TMA form squashes scores")
     if kernel == "tma" and not _tma_decode_applies(q, page):
         raise KernelError(f"paged_attention_decode: the TMA form takes bf16, head size 64 or 128 "
                           f"and a page of 8, 16, 32 or 64 keys (got {q.dtype}, {hd}, {page})")
@@ -663,10 +666,10 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
         part_o = torch.empty((S, heads, splits, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((S, heads, splits, 2), dtype=torch.float32, device=q.device)
     if kernel == "tma":
-        code = lib.ix_paged_attention_decode_tma(
+        code = lib.ix_paged_attention_decode_tma_capped(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), P, _ptr(block_table), _ptr(kv_len),
             _ptr(part_o), _ptr(part_ml), _ptr(out), S, heads, kvh, hd, page,
-            block_table.shape[1], window, ctypes.c_float(scale), splits,
+            block_table.shape[1], window, ctypes.c_float(scale), ctypes.c_float(softcap), splits,
             _ptr(_tc_status(q.device)), _stream())
     else:
         entry = (lib.ix_paged_attention_decode_scalar if kernel == "scalar"
@@ -697,7 +700,7 @@ def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
                             block_table: torch.Tensor, cu_q: torch.Tensor, q_pos0: torch.Tensor,
                             window: int, scale: float, kernel: Optional[str] = None,
                             out: Optional[torch.Tensor] = None, splits: Optional[int] = None,
-                            max_kv_len: Optional[int] = None):
+                            max_kv_len: Optional[int] = None, softcap: float = 0.0):
     """Tensor-core attention for a ragged batch: sequence s brings the queries
     q[cu_q[s]:cu_q[s+1]] at positions q_pos0[s], q_pos0[s]+1, ...  ``kernel`` picks a
     form ("tc", "mma"); None takes the fastest that applies.  ``splits`` (tcgen05 form):
@@ -725,6 +728,8 @@ def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
         kernel = "tc" if USE_TCGEN05_ATTENTION and _tc_prefill_applies(q, page) else "mma"
     if kernel not in ("tc", "mma"):
         raise KernelError(f"paged_attention_prefill: no kernel form {kernel!r}")
+    if softcap > 0 and kernel != "tc":
+        raise KernelError("paged_attention_prefill: only the tcgen05 form squashes scores")
     if kernel == "tc" and not _tc_prefill_applies(q, page):
         raise KernelError(f"paged_attention_prefill: the tcgen05 form takes bf16, head size 64 "
                           f"or 128 and a page of 8, 16, 32 or 64 keys (got {q.dtype}, {hd}, "
@@ -747,11 +752,18 @@ def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
             part_o = torch.empty((T, heads, splits, hd), dtype=torch.float32, device=q.device)
             part_ml = torch.empty((T, heads, splits, 2), dtype=torch.float32, device=q.device)
             launches = 2
-        code = _lib().ix_paged_attention_prefill_tc(
-            _ptr(q), _ptr(k_cache), _ptr(v_cache), P, _ptr(block_table), _ptr(cu_q),
-            _ptr(q_pos0), _ptr(out), T, S, heads, kvh, hd, page, block_table.shape[1], window,
-            ctypes.c_float(scale), splits, _ptr(part_o), _ptr(part_ml),
-            _ptr(_tc_status(q.device)), _stream())
+        if softcap > 0:
+            code = _lib().ix_paged_attention_prefill_tc_capped(
+                _ptr(q), _ptr(k_cache), _ptr(v_cache), P, _ptr(block_table), _ptr(cu_q),
+                _ptr(q_pos0), _ptr(out), T, S, heads, kvh, hd, page, block_table.shape[1],
+                window, ctypes.c_float(scale), ctypes.c_float(softcap), splits, _ptr(part_o),
+                _ptr(part_ml), _ptr(_tc_status(q.device)), _stream())
+        else:
+            code = _lib().ix_paged_attention_prefill_tc(
+                _ptr(q), _ptr(k_cache), _ptr(v_cache), P, _ptr(block_table), _ptr(cu_q),
+                _ptr(q_pos0), _ptr(out), T, S, heads, kvh, hd, page, block_table.shape[1],
+                window, ctypes.c_float(scale), splits, _ptr(part_o), _ptr(part_ml),
+                _ptr(_tc_status(q.device)), _stream())
     else:
         code = _lib().ix_paged_attention_prefill(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(cu_q), _ptr(q_pos0),
@@ -773,12 +785,15 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     single tokens go to the split-KV kernel; everything else, and head sizes the
     tuned kernels do not take, to the general kernel."""
     hd = q.shape[2]
-    if softcap > 0:
+    page = k_cache.shape[2]
+    if softcap > 0 and not (scale > 0 and USE_TMA_DECODE and _tma_decode_applies(q, page)
+                            and USE_TCGEN05_ATTENTION and _tc_prefill_applies(q, page)):
+        # of the tuned kernels only the TMA decode form and the tcgen05 prompt form squash
         return _paged_attention_softcap(q, k_cache, v_cache, block_table, step, window, scale,
                                         softcap)
     if step.all_decode and hd in _DECODE_HEAD_SIZES.get(q.dtype, ()):
         return paged_attention_decode(q, k_cache, v_cache, block_table, step.kv_len,
-                                      step.max_kv_len, window, scale)
+                                      step.max_kv_len, window, scale, softcap=softcap)
     if hd in _PREFILL_HEAD_SIZES.get(q.dtype, ()):
         nd = getattr(step, "num_decode_seqs", 0)
         if 0 < nd < step.num_seqs and getattr(step, "cu_q_prompt", None) is not None:
@@ -786,13 +801,14 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
             # which streams their keys at full rate, the prompt portions to the tiled one
             out = torch.empty_like(q)
             paged_attention_decode(q[:nd], k_cache, v_cache, block_table[:nd], step.kv_len[:nd],
-                                   step.max_kv_len, window, scale, out=out[:nd])
+                                   step.max_kv_len, window, scale, out=out[:nd], softcap=softcap)
             paged_attention_prefill(q[nd:], k_cache, v_cache, block_table[nd:],
                                     step.cu_q_prompt, step.q_pos0[nd:], window, scale,
-                                    out=out[nd:], max_kv_len=step.max_kv_len)
+                                    out=out[nd:], max_kv_len=step.max_kv_len, softcap=softcap)
             return out
         return paged_attention_prefill(q, k_cache, v_cache, block_table, step.cu_q, step.q_pos0,
-                                       window, scale, max_kv_len=step.max_kv_len)
+                                       window, scale, max_kv_len=step.max_kv_len,
+                                       softcap=softcap)
     if (step.num_tokens >= TILED_ATTENTION_MIN_QUERIES * step.num_seqs
             and _lib().ix_paged_attention_tiled_applies(hd)
             and getattr(step, "cu_q", None) is not None):

@@ -124,7 +124,8 @@ class ParallelBlock:
         if f_norm is None:
             if hasattr(pending, "materialize") and not getattr(a_norm, "accepts_pending", False):
                 pending = pending.materialize()
-            return self.mixer.forward(a_norm.forward(resid, pending), step, cache)
+            a = self.mixer.forward(a_norm.forward(resid, pending), step, cache)
+            return PendingSum(terms=[a], dtype=self.ctx.dtype)
         if hasattr(a_norm, "forward_pair") and hasattr(f_norm, "gain") and \
                 a_norm.spec.eps == f_norm.spec.eps:
             na, nf = a_norm.forward_pair(resid, pending, f_norm)
