@@ -19,7 +19,9 @@ live requests) over its time, against the measured copy bandwidth.
 
 ``--designs`` is a separate report and leaves the default line alone: one JSON line per
 size (``--design-sizes 1k,2k,4k``) with the prompt and decode throughput of the Zuzisun
-design beside Qwen2-MoE with every layer dense at equal sizes.
+design beside Qwen2-MoE with every layer dense at equal sizes; ``--design tinapel`` does the
+same for the Tinapel design beside Qwen2-MoE with the same experts (``--design-pattern``
+names the mixers of its layers).
 
 A decode step's working set (gigabytes of weights and cache) is far larger than the
 126 MB L2, so nothing stays resident between timed iterations.
@@ -803,6 +805,48 @@ def design_configs(z, layers):
     return new, twin
 
 
+# `--designs --design tinapel`: the Tinapel design (wkv time mixing, gated linear attention
+# and attention with tied keys/values in parallel with a mixture of experts) beside
+# Qwen2-MoE at equal width, depth, attention heads, experts and feed-forward widths.
+TINAPEL_SIZES = {
+    # attention heads of 128 over `kv` key/value heads; wkv heads of 64; gated linear
+    # attention heads with 64 key and 128 value entries
+    "1k": dict(width=1024, heads=8, kv=2, experts=16, top=2, ff=512, shared=2048),
+    "2k": dict(width=2048, heads=16, kv=4, experts=32, top=4, ff=1024, shared=4096),
+    "4k": dict(width=4096, heads=32, kv=8, experts=32, top=4, ff=1408, shared=5632),
+}
+
+
+def tinapel_configs(z, layers, pattern):
+    import math
+    W = z["width"]
+    mlp = {"kind": "moe", "expert": {"ff": z["ff"]},
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 1.0},
+           "shared": {"ff": z["shared"]}}
+    kinds = {
+        "wkv": {"type": "wkv", "mixer": {"heads": W // 64, "dim": 64, "rank": 64}, "mlp": mlp},
+        "gla": {"type": "gla", "mixer": {"heads": W // 128, "dim": 64, "vdim": 128, "tau": 16.0,
+                                         "rank": 16}, "mlp": mlp},
+        "attention": {"type": "attention",
+                      "mixer": {"heads": z["heads"], "kv_heads": z["kv"], "dim": 128, "vdim": 128,
+                                "scale": 1.0 / math.sqrt(128.0), "softcap": 50.0,
+                                "q_temp": {"coef": 0.1, "every": 1024}}, "mlp": mlp},
+    }
+    new = {"architecture": "Tinapel", "vocab": DESIGN_VOCAB, "width": W,
+           "embedding": {"scale": math.sqrt(W)}, "norm": {"eps": 1e-6},
+           "layers": [kinds[pattern[i % len(pattern)]] for i in range(layers)]}
+    twin = {"architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",
+            "num_hidden_layers": layers, "hidden_size": W,
+            "num_attention_heads": z["heads"], "num_key_value_heads": z["kv"],
+            "head_dim": 128, "num_experts": z["experts"], "num_experts_per_tok": z["top"],
+            "moe_intermediate_size": z["ff"], "shared_expert_intermediate_size": z["shared"],
+            "intermediate_size": z["shared"], "decoder_sparse_step": 1,
+            "mlp_only_layers": [], "norm_topk_prob": True,
+            "vocab_size": DESIGN_VOCAB, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+            "use_sliding_window": False, "tie_word_embeddings": True, "torch_dtype": "bfloat16"}
+    return new, twin
+
+
 def designs(args):
     """One JSON line per size: prompt tokens/s (one prompt of --prefill-tokens, default
     2048) and decode tokens/s (--batch sequences at --context) of both designs, device
@@ -811,13 +855,23 @@ def designs(args):
     layers = args.layers or 4
     prompt = args.prefill_tokens or 2048
     B = args.batch
-    for name in (args.design_sizes.split(",") if args.design_sizes else list(DESIGN_SIZES)):
-        z = DESIGN_SIZES[name]
+    tinapel = args.design == "tinapel"
+    sizes = TINAPEL_SIZES if tinapel else DESIGN_SIZES
+    first, second = ("tinapel", "qwen2_moe") if tinapel else ("zuzisun", "qwen2_dense")
+    for name in (args.design_sizes.split(",") if args.design_sizes else list(sizes)):
+        z = sizes[name]
         C = args.context or 4096
         row = {"size": name, "layers": layers, "width": z["width"], "heads": z["heads"],
-               "ff": z["ff"], "window": z["window"], "prompt_tokens": prompt, "batch": B,
+               "ff": z["ff"], "prompt_tokens": prompt, "batch": B,
                "context": C, "dtype": "bf16", "data": "synthetic, random weights"}
-        for label, cfg in zip(("zuzisun", "qwen2_dense"), design_configs(z, layers)):
+        if tinapel:
+            pattern = args.design_pattern.split(",")
+            row["pattern"] = pattern
+            pair = tinapel_configs(z, layers, pattern)
+        else:
+            row["window"] = z["window"]
+            pair = design_configs(z, layers)
+        for label, cfg in zip((first, second), pair):
             extra = args.steps + args.warmup + 8
             rt = make_runtime(cfg, max(B, 1), max(C + extra, prompt) + 64, 0,
                               use_graphs=not args.no_graphs, max_slots=B + 1)
@@ -832,10 +886,10 @@ def designs(args):
                               for n in needs if hasattr(n, "bytes_per_token"))}
             del rt
             torch.cuda.empty_cache()
-        row["prefill_ratio"] = round(row["zuzisun"]["prefill_tok_s"]
-                                     / row["qwen2_dense"]["prefill_tok_s"], 3)
-        row["decode_ratio"] = round(row["zuzisun"]["decode_tok_s"]
-                                    / row["qwen2_dense"]["decode_tok_s"], 3)
+        row["prefill_ratio"] = round(row[first]["prefill_tok_s"]
+                                     / row[second]["prefill_tok_s"], 3)
+        row["decode_ratio"] = round(row[first]["decode_tok_s"]
+                                    / row[second]["decode_tok_s"], 3)
         print(json.dumps(row), flush=True)
     return 0
 
@@ -882,6 +936,10 @@ def main(argv=None):
                          "with dense layers at equal sizes (random weights); --layers (4), "
                          "--batch, --context (4096), --prefill-tokens (2048) apply")
     ap.add_argument("--design-sizes", default="", help="with --designs: of 1k,2k,4k (all)")
+    ap.add_argument("--design", default="zuzisun", choices=["zuzisun", "tinapel"],
+                    help="with --designs: which design stands beside its closest model")
+    ap.add_argument("--design-pattern", default="wkv,gla,attention,attention",
+                    help="with --design tinapel: the mixers of the layers, repeated")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return reference_arm()

@@ -11,6 +11,9 @@
     python -m inferx_b200.kernels.microbench latent_attn --tokens 2048 --rank 512 --rot-dim 64 [--form mma|general]
     python -m inferx_b200.kernels.microbench latent_attn --tokens 1 --batch 8 --context 4096
     python -m inferx_b200.kernels.microbench rowwise --tokens 4096 --hidden 2048 --inter 5632
+    python -m inferx_b200.kernels.microbench recurrent --tokens 4096 --batch 1 --hidden 2048 --head-dim 64
+    python -m inferx_b200.kernels.microbench recurrent --tokens 64 --batch 64 --hidden 2048 --head-dim 64
+    python -m inferx_b200.kernels.microbench attn_prefill --tokens 2048 --softcap 50
 
 Each case runs one kernel face at Qwen1.5-MoE-A2.7B sizes (or the sizes given),
 cycling through enough copies of its inputs that consecutive iterations do not
@@ -85,7 +88,8 @@ def attn_decode(args):
 
     def fn(i):
         ops.paged_attention_decode(q, kcs[i], vcs[i], bt, kv_len, C, args.window, scale,
-                                   splits=args.splits or None, kernel=args.form or None)
+                                   splits=args.splits or None, kernel=args.form or None,
+                                   softcap=args.softcap)
     us = _time(fn, n, args.iters)
     span = min(C, args.window) if args.window else C
     nbytes = B * span * kvh * hd * 2 * 2
@@ -219,7 +223,8 @@ def attn_prefill(args):
             ops.paged_attention_tiled(q, kc, vc, bt, step.cu_q, step.q_pos0, args.window, scale)
         else:
             ops.paged_attention_prefill(q, kc, vc, bt, step.cu_q, step.q_pos0, args.window, scale,
-                                        kernel=args.form or None, splits=args.splits or None)
+                                        kernel=args.form or None, splits=args.splits or None,
+                                        softcap=args.softcap)
     us = _time(fn, 1, args.iters)
     flops = 4 * heads * hd * (T * T / 2 + T * (C - T))
     return {"case": "attn_prefill", "tokens": T, "context": C, "heads": heads, "head_dim": hd,
@@ -312,10 +317,87 @@ def rowwise(args):
     return out
 
 
+def recurrent(args):
+    """The kernels of the recurrent mixers and of the parallel arrangement: ``--tokens`` rows
+    of ``--hidden`` as one prompt (``--batch`` 1) or as that many sequences of one token
+    (``--batch`` = ``--tokens``); heads of ``--head-dim`` key and value entries.  Achieved
+    GB/s over the bytes the operation has to move."""
+    from . import ops
+    T, W, B = args.tokens, args.hidden, max(1, args.batch)
+    K = V = args.head_dim
+    H = W // K
+    R = args.rank if args.rank <= 128 else 64
+    dt = torch.bfloat16
+    n = max(2, min(8, _copies(T * W * 14)))
+    resid = [torch.randn(T, W, device="cuda") for _ in range(n)]
+    d32 = [torch.randn(T, W, device="cuda") for _ in range(n)]
+    d16 = [torch.randn(T, W, device="cuda", dtype=dt) for _ in range(n)]
+    x16 = [torch.randn(T, W, device="cuda", dtype=dt) for _ in range(n)]
+    gain = torch.ones(W, device="cuda")
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    per = T // B
+    step = types.SimpleNamespace(
+        cu_q=i32([i * per for i in range(B + 1)]), num_seqs=B,
+        seq_of_token=torch.arange(T, dtype=torch.int32, device="cuda") // per,
+        state_slot=torch.arange(B, dtype=torch.int32, device="cuda"),
+        positions=torch.arange(T, dtype=torch.int32, device="cuda") % per)
+    mu = torch.rand(5, W, device="cuda")
+    prev = torch.zeros(B, W, device="cuda")
+    states = [torch.zeros(B, H, K, V, device="cuda") for _ in range(n)]
+    qkv = [torch.randn(3, T, H * K, device="cuda", dtype=dt) * 0.1 for _ in range(n)]
+    decay = [torch.rand(T, H * K, device="cuda") * 0.1 + 0.9 for _ in range(n)]
+    u = torch.randn(H, K, device="cuda")
+    low = [torch.randn(T, R, device="cuda") for _ in range(n)]
+    w2 = torch.randn(H * K, R, device="cuda") * 0.1
+    b = torch.zeros(H * K, device="cuda")
+    o = [torch.randn(T, H, V, device="cuda") for _ in range(n)]
+    G = max(1, H // 4)
+    qk = [torch.randn(T, (H + G) * K, device="cuda", dtype=dt) for _ in range(n)]
+    pages = -(-T // 16) + 1
+    kc = torch.zeros(pages, G, 16, K, device="cuda", dtype=dt)
+    vc = torch.zeros_like(kc)
+    slots = torch.arange(T, dtype=torch.int32, device="cuda")
+    state_bytes = 2 * B * H * K * V * 4
+    cases = {
+        "add_rmsnorm_sum(2 terms, 2 norms)": (
+            lambda i: ops.add_rmsnorm_sum(resid[i], [d32[i], d16[i]], None, (gain, gain), 1e-5, dt),
+            (8 + 4 + 2 + 4) * T * W),
+        "add_rmsnorm": (lambda i: ops.add_rmsnorm(resid[i], d16[i], gain, 1e-5, dt), 12 * T * W),
+        "shift_mix(5)": (lambda i: ops.shift_mix(x16[i], mu, prev, step), 12 * T * W),
+        "lowrank_decay": (lambda i: ops.lowrank_decay(low[i], w2, b, "exp_exp_tanh"),
+                          4 * T * (R + H * K)),
+        "linear_recurrence(bonus)": (
+            lambda i: ops.linear_recurrence(qkv[i][0], qkv[i][1], qkv[i][2], decay[i], u,
+                                            states[i], step, H, K, V, 1.0, True),
+            T * H * (3 * K * 2 + K * 4 + V * 4) + state_bytes),
+        "linear_recurrence(plain)": (
+            lambda i: ops.linear_recurrence(qkv[i][0], qkv[i][1], qkv[i][2], decay[i], None,
+                                            states[i], step, H, K, V, 0.125, False),
+            T * H * (3 * K * 2 + K * 4 + V * 4) + state_bytes),
+        "head_norm_gate": (lambda i: ops.head_norm_gate(o[i], gain, x16[i], 1e-5, dt),
+                           (4 + 2 + 2) * T * W),
+        "qk_norm_append": (
+            lambda i: ops.qk_norm_append(qk[i], gain[:K], gain[:K], step.positions, H, G, K, 1e-5,
+                                         0.1, 128, kc, vc, slots),
+            T * K * (2 * (H + G) + 2 * H + 4 * G)),
+    }
+    out = {"case": "recurrent", "tokens": T, "sequences": B, "hidden": W, "heads": H,
+           "head_dim": K, "rank": R}
+    for name, (fn, nbytes) in cases.items():
+        us = _time(fn, n, args.iters)
+        out[name] = {"us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1)}
+    flops = 2 * 3 * T * H * K * V      # decay, outer product and read-out per state entry
+    us = out["linear_recurrence(bonus)"]["us"]
+    out["linear_recurrence(bonus)"]["TFLOPs_fp32"] = round(flops / us / 1e6, 2)
+    return out
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("case", choices=["attn_decode", "grouped", "dense", "attn_prefill", "router",
-                                     "qkv", "latent_attn", "rowwise"])
+                                     "qkv", "latent_attn", "rowwise", "recurrent"])
+    ap.add_argument("--softcap", type=float, default=0.0,
+                    help="attn_decode, attn_prefill: squash scores to softcap * tanh(s / softcap)")
     ap.add_argument("--rank", type=int, default=512, help="latent_attn: entries of the latent")
     ap.add_argument("--rot-dim", type=int, default=64, help="latent_attn: rotated key entries")
     ap.add_argument("--iters", type=int, default=50)

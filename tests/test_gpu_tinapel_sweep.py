@@ -1,0 +1,80 @@
+"""The Tinapel design over configurations drawn at random: every size and option varies at
+once (layer kinds in any order, head sizes from 3 to 128, odd widths and vocabularies, 1
+to 12 experts with 1 to all chosen, layers without feed-forward, loops over any stretch
+of layers, with and without squashed scores and query temperature, pages of 4 to 64
+tokens).  Each drawn model replays one trace in float32 and in bfloat16 against the
+plain model.  The seeds are fixed, so the cases are the same on every run."""
+import random
+
+import pytest
+
+import model_cases as mc
+import tinapel_cases as tc
+import traces
+from inferx_b200.engine.replay import ReplaySession
+
+pytestmark = pytest.mark.gpu
+
+
+def draw_mlp(rng):
+    if rng.random() < 0.15:
+        return None
+    experts = rng.choice([1, 2, 3, 4, 5, 8, 12])
+    top = rng.randrange(1, experts + 1)
+    return tc.moe(experts, top, rng.choice([8, 24, 40, 66, 100]), rng.choice([1.0, 0.5, 2.5]),
+                  shared=rng.choice([0, 16, 50, 96]))
+
+
+def draw_layer(rng):
+    kind = rng.choice(["wkv", "gla", "attention"])
+    if kind == "wkv":
+        return tc.wkv(rng.choice([1, 2, 3, 5]), rng.choice([3, 8, 16, 24, 33, 64, 128]),
+                      rng.choice([1, 4, 16, 40]), draw_mlp(rng))
+    if kind == "gla":
+        return tc.gla(rng.choice([1, 2, 4, 6]), rng.choice([4, 8, 20, 32, 64, 100]),
+                      rng.choice([4, 12, 32, 64, 128, 37]), rng.choice([1.0, 4.0, 16.0]),
+                      rng.choice([2, 8, 16, 33]), draw_mlp(rng))
+    kv = rng.choice([1, 1, 2, 3])
+    dim = rng.choice([9, 16, 20, 32, 64, 64, 96, 128, 128])
+    return tc.attention(kv * rng.choice([1, 2, 4]), kv, dim, rng.choice([0.1, 0.3, dim ** -0.5]),
+                        softcap=rng.choice([0.0, 3.0, 30.0, 50.0]),
+                        q_temp=rng.choice([None, (0.3, 5), (0.1, 64), (0.7, 1)]),
+                        mlp=draw_mlp(rng))
+
+
+def draw_config(rng):
+    n = rng.randrange(1, 5)
+    cfg = {"architecture": "Tinapel", "vocab": rng.choice([37, 101, 256, 500, 777]),
+           "width": rng.choice([24, 40, 50, 64, 72, 100, 136, 192, 250, 264]),
+           "embedding": {"scale": rng.choice([1.0, 4.0, 11.3])},
+           "norm": {"eps": rng.choice([1e-6, 1e-5, 3e-4])},
+           "layers": [draw_layer(rng) for _ in range(n)]}
+    if rng.random() < 0.7:
+        a = rng.randrange(0, n)
+        b = rng.randrange(a + 1, n + 1)
+        cfg["loop"] = {"start": a, "stop": b, "times": rng.choice([1, 2, 2, 3])}
+    return cfg
+
+
+SEEDS = [1, 3, 4, 8, 9, 15, 21, 22, 30, 41, 47, 52, 63, 71, 90, 101]
+
+
+@pytest.mark.parametrize("seed", SEEDS)
+def test_drawn_configuration_matches_plain(tmp_path, seed):
+    rng = random.Random(seed)
+    cfg = draw_config(rng)
+    page = rng.choice([4, 8, 16, 16, 32, 64])
+    lengths = [rng.randrange(1, 120) for _ in range(rng.randrange(2, 6))]
+    kind = rng.choice(["tail", "portions", "mixed", "mixed"])
+    what = (f"seed {seed}: {[l['type'] for l in cfg['layers']]}, loop {cfg.get('loop')}, width "
+            f"{cfg['width']}, vocab {cfg['vocab']}, page {page}, {kind}")
+    for dtype in ("float32", "bfloat16"):
+        d = tc.make_model_dir(cfg, tmp_path / dtype, seed, dtype=dtype)
+        reqs = tc.make_requests(cfg, lengths, seed)
+        ref = tc.reference_rows(d, reqs)
+        steps = mc.TRACE_KINDS[kind](reqs)
+        sess = ReplaySession(d, dtype, traces.peak_tokens(steps), page_size=page, max_live=4,
+                             use_graphs=rng.random() < 0.5)
+        rows = mc.run_trace(sess, steps)
+        sess.executor.poll_errors()
+        mc.compare(rows, ref, tc.bound_for(dtype, d, reqs), f"{what}, {dtype}")
