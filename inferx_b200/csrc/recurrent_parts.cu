@@ -3,7 +3,7 @@
 //   shift mix          out[m][t] = x[t] + (x[t-1] - x[t]) * mu[m] for several mu at once;
 //                      the row before a sequence's first token of the step comes from
 //                      per-request state, which then takes the sequence's last row
-//   low-rank decay     z[t][c] = b[c] + sum_r act(x[t][r]) * w2[c][r], then
+//   low-rank decay     z[t][c] = b[c] + sum_r act(x[t][r]) * w2t[r][c], then
 //                        form 0:  exp(-exp(z)),            act = tanh
 //                        form 1:  sigmoid(z)^(1/tau),       act = identity
 //   linear recurrence  per (sequence, head), tokens in order, S [K][V] in fp32:
@@ -59,15 +59,16 @@ IX_API int ix_shift_mix(const void* x, int dtype, const float* mu, float* state,
 
 // ---------------------------------------------------------------------------
 // low-rank decay.  A block takes LRD_TOKENS tokens and LRD_THREADS channels; a thread
-// reads its channel's row of w2 once for all of the block's tokens.  A token's sum runs
+// reads its channel's column of the transposed matrix w2t [R][C] once for all of the
+// block's tokens (neighbouring threads read neighbouring addresses).  A token's sum runs
 // over r in ascending order whatever else is in the block.
 // ---------------------------------------------------------------------------
-#define LRD_TOKENS 8
+#define LRD_TOKENS 16
 #define LRD_THREADS 128
 
 template <typename TX>
 __global__ void lowrank_decay_kernel(const TX* __restrict__ x, long long ldx,
-                                     const float* __restrict__ w2, const float* __restrict__ b,
+                                     const float* __restrict__ w2t, const float* __restrict__ b,
                                      float* __restrict__ out, int T, int C, int R, int form,
                                      float inv_tau) {
   extern __shared__ float act[];   // [LRD_TOKENS][R]
@@ -84,9 +85,8 @@ __global__ void lowrank_decay_kernel(const TX* __restrict__ x, long long ldx,
   float z[LRD_TOKENS];
 #pragma unroll
   for (int j = 0; j < LRD_TOKENS; ++j) z[j] = 0.f;
-  const float* wr = w2 + (size_t)c * R;
   for (int r = 0; r < R; ++r) {
-    const float w = wr[r];
+    const float w = w2t[(size_t)r * C + c];
 #pragma unroll
     for (int j = 0; j < LRD_TOKENS; ++j)
       if (j < nt) z[j] += act[j * R + r] * w;
@@ -107,7 +107,7 @@ __global__ void lowrank_decay_kernel(const TX* __restrict__ x, long long ldx,
   }
 }
 
-IX_API int ix_lowrank_decay(const void* x, int x_dtype, long long ldx, const float* w2,
+IX_API int ix_lowrank_decay(const void* x, int x_dtype, long long ldx, const float* w2t,
                             const float* b, float* out, int T, int C, int R, int form, float tau,
                             cudaStream_t stream) {
   if (T <= 0) return IX_OK;
@@ -118,21 +118,34 @@ IX_API int ix_lowrank_decay(const void* x, int x_dtype, long long ldx, const flo
   if (grid.y > 65535) return IX_ERR_SIZE;
   IX_DISPATCH_DTYPE(x_dtype, TX,
                     ix_launch(lowrank_decay_kernel<TX>, grid, dim3(LRD_THREADS), smem, stream,
-                              (const TX*)x, ldx, w2, b, out, T, C, R, form, 1.0f / tau));
+                              (const TX*)x, ldx, w2t, b, out, T, C, R, form, 1.0f / tau));
   return ix_launch_status();
 }
 
 // ---------------------------------------------------------------------------
-// linear recurrence.  grid (ceil(V / 32), heads, sequences); a block is 32 value columns
-// times KS slices of the key channels (one warp per slice).  A thread keeps its KPT
-// entries of one state column in registers from the sequence's first token of the step
-// to its last; key channels do not interact, so the slices walk a chunk of tokens without
-// meeting, leave their partial outputs in shared memory, and the partials are added in
-// ascending slice order.  The order of every sum is fixed by (K, KS) alone: a position's
-// output does not depend on how its sequence was cut into steps or chunks.
+// linear recurrence.  grid (ceil(V / 32) * segments, heads, sequences); a block is 32
+// value columns times KS slices of the key channels (one warp per slice).  A thread keeps
+// its KPT entries of one state column in registers while it walks its tokens; key channels
+// do not interact, so the slices walk a chunk of tokens without meeting, leave their
+// partial outputs in shared memory, and the partials are added in ascending slice order.
+//
+// Three forms of the walk:
+//   whole (segments = 1)  a block walks all of its sequence's tokens of the step, from the
+//                         state in the slot to the state it leaves there.  The order of
+//                         every sum is fixed by (K, KS): a position's output does not
+//                         depend on how its sequence was cut into steps or chunks.
+//   local                 long prompts are cut into segments of seg_len tokens that are
+//                         walked side by side.  The first pass walks every segment but a
+//                         sequence's last from a zero state and leaves in scratch the
+//                         state it ends with and the product of its decays (entry seg + 1);
+//                         entry 0 takes the state from the slot.
+//   joined                the second pass rebuilds a segment's start state from the
+//                         entries before it, S <- P_i S + S_i in ascending i, then walks
+//                         the segment with outputs; the last segment leaves the state.
 // ---------------------------------------------------------------------------
 #define LR_COLS 32
 #define LR_CHUNK 16
+enum { LR_WHOLE = 0, LR_LOCAL = 1, LR_JOINED = 2 };
 
 template <typename TA, int KPT, bool BONUS>
 __global__ void __launch_bounds__(LR_COLS * 8)
@@ -141,7 +154,8 @@ linear_recurrence_kernel(const TA* __restrict__ q, long long ldq, const TA* __re
                          const float* __restrict__ decay, const float* __restrict__ bonus,
                          float* __restrict__ state, const int* __restrict__ cu_q,
                          const int* __restrict__ state_slot, float* __restrict__ out, int H,
-                         int K, int V, int KS, float q_scale) {
+                         int K, int V, int KS, float q_scale, int mode, int seg_len, int nseg,
+                         float* __restrict__ scr_s, float* __restrict__ scr_p) {
   extern __shared__ float sm[];
   float* q_s = sm;                       // [LR_CHUNK][K]
   float* k_s = q_s + LR_CHUNK * K;       // [LR_CHUNK][K]
@@ -150,27 +164,56 @@ linear_recurrence_kernel(const TA* __restrict__ q, long long ldq, const TA* __re
   float* part = v_s + LR_CHUNK * LR_COLS;  // [KS][LR_CHUNK][LR_COLS]
   IX_PDL_WAIT();
   const int lane = threadIdx.x & 31, ks = threadIdx.x >> 5;
-  const int v0 = blockIdx.x * LR_COLS, h = blockIdx.y, s = blockIdx.z;
+  const int vtiles = (V + LR_COLS - 1) / LR_COLS;
+  const int seg = blockIdx.x / vtiles;
+  const int v0 = (blockIdx.x % vtiles) * LR_COLS, h = blockIdx.y, s = blockIdx.z;
   const int col = v0 + lane;
   const bool col_ok = col < V;
-  const int t_begin = cu_q[s], t_end = cu_q[s + 1];
+  const int seq_begin = cu_q[s], seq_end = cu_q[s + 1];
+  const int nseg_s = mode == LR_WHOLE ? 1 : (seq_end - seq_begin + seg_len - 1) / seg_len;
+  if (seg >= nseg_s) return;
+  const int t_begin = mode == LR_WHOLE ? seq_begin : seq_begin + seg * seg_len;
+  const int t_end = mode == LR_WHOLE ? seq_end : min(seq_end, t_begin + seg_len);
   float* st = state + ((size_t)state_slot[s] * H + h) * K * V;
+  float* my_s = scr_s + ((size_t)s * H + h) * nseg * K * V;    // entries of this (sequence, head)
+  float* my_p = scr_p + ((size_t)s * H + h) * nseg * K;
   const int kk0 = ks * KPT;
+  const bool walks = mode != LR_LOCAL || seg < nseg_s - 1;
 
-  float S[KPT], u[KPT];
+  float S[KPT], u[KPT], P[KPT];
 #pragma unroll
   for (int i = 0; i < KPT; ++i) {
     const int kk = kk0 + i;
-    S[i] = (kk < K && col_ok) ? st[(size_t)kk * V + col] : 0.f;
+    const bool ok = kk < K && col_ok;
+    P[i] = 1.f;
     u[i] = (BONUS && kk < K) ? bonus[(size_t)h * K + kk] : 0.f;
+    if (mode == LR_WHOLE) {
+      S[i] = ok ? st[(size_t)kk * V + col] : 0.f;
+    } else if (mode == LR_LOCAL) {
+      if (seg == 0 && ok) my_s[(size_t)kk * V + col] = st[(size_t)kk * V + col];
+      S[i] = 0.f;
+    } else {
+      S[i] = ok ? my_s[(size_t)kk * V + col] : 0.f;
+    }
   }
+  if (mode == LR_JOINED) {
+    for (int e = 1; e <= seg; ++e) {
+#pragma unroll
+      for (int i = 0; i < KPT; ++i) {
+        const int kk = kk0 + i;
+        if (kk < K && col_ok)
+          S[i] = my_p[(size_t)e * K + kk] * S[i] + my_s[((size_t)e * K + kk) * V + col];
+      }
+    }
+  }
+  if (!walks) return;
 
   for (int t0 = t_begin; t0 < t_end; t0 += LR_CHUNK) {
     const int n = min(LR_CHUNK, t_end - t0);
     for (int i = threadIdx.x; i < n * K; i += blockDim.x) {
       const int c = i / K, kk = i % K;
       const size_t t = (size_t)(t0 + c);
-      q_s[i] = to_f32(q[t * ldq + (size_t)h * K + kk]) * q_scale;
+      if (mode != LR_LOCAL) q_s[i] = to_f32(q[t * ldq + (size_t)h * K + kk]) * q_scale;
       k_s[i] = to_f32(k[t * ldk + (size_t)h * K + kk]);
       w_s[i] = decay[(t * H + h) * K + kk];
     }
@@ -179,6 +222,22 @@ linear_recurrence_kernel(const TA* __restrict__ q, long long ldq, const TA* __re
       v_s[i] = (v0 + j < V) ? to_f32(v[(size_t)(t0 + c) * ldv + (size_t)h * V + v0 + j]) : 0.f;
     }
     __syncthreads();
+    if (mode == LR_LOCAL) {
+      for (int c = 0; c < n; ++c) {
+        const float vj = v_s[c * LR_COLS + lane];
+        const float* kc = k_s + c * K + kk0;
+        const float* wc = w_s + c * K + kk0;
+#pragma unroll
+        for (int i = 0; i < KPT; ++i) {
+          if (kk0 + i < K) {
+            S[i] = wc[i] * S[i] + kc[i] * vj;
+            P[i] *= wc[i];
+          }
+        }
+      }
+      __syncthreads();
+      continue;
+    }
     for (int c = 0; c < n; ++c) {
       const float vj = v_s[c * LR_COLS + lane];
       const float* qc = q_s + c * K + kk0;
@@ -211,6 +270,16 @@ linear_recurrence_kernel(const TA* __restrict__ q, long long ldq, const TA* __re
     }
     __syncthreads();
   }
+  if (mode == LR_LOCAL) {
+#pragma unroll
+    for (int i = 0; i < KPT; ++i) {
+      const int kk = kk0 + i;
+      if (kk < K && col_ok) my_s[((size_t)(seg + 1) * K + kk) * V + col] = S[i];
+      if (kk < K && v0 == 0 && lane == 0) my_p[(size_t)(seg + 1) * K + kk] = P[i];
+    }
+    return;
+  }
+  if (mode == LR_JOINED && seg != nseg_s - 1) return;
 #pragma unroll
   for (int i = 0; i < KPT; ++i) {
     const int kk = kk0 + i;
@@ -220,39 +289,55 @@ linear_recurrence_kernel(const TA* __restrict__ q, long long ldq, const TA* __re
 
 IX_API int ix_linear_recurrence_max_dim() { return 8 * 64; }
 
+// Floats of scratch the segmented walk needs for `S` sequences cut into `nseg` segments.
+IX_API long long ix_linear_recurrence_scratch_floats(int S, int H, int K, int V, int nseg) {
+  return nseg <= 1 ? 0 : (long long)S * H * nseg * ((long long)K * V + K);
+}
+
 template <typename TA, int KPT>
 static void launch_recurrence(const void* q, long long ldq, const void* k, long long ldk,
                               const void* v, long long ldv, const float* decay,
                               const float* bonus, float* state, const int* cu_q,
                               const int* state_slot, float* out, int S, int H, int K, int V,
-                              int KS, float q_scale, int bonus_form, size_t smem,
-                              cudaStream_t stream) {
-  dim3 grid((V + LR_COLS - 1) / LR_COLS, H, S), block(LR_COLS * KS);
-  if (bonus_form) {
+                              int KS, float q_scale, int bonus_form, size_t smem, int seg_len,
+                              int nseg, float* scratch, cudaStream_t stream) {
+  const int vtiles = (V + LR_COLS - 1) / LR_COLS;
+  dim3 grid(vtiles * nseg, H, S), block(LR_COLS * KS);
+  float* scr_s = scratch;
+  float* scr_p = scratch ? scratch + (size_t)S * H * nseg * K * V : nullptr;
+  auto go = [&](auto kern) {
     if (smem > 48 * 1024)
-      cudaFuncSetAttribute(linear_recurrence_kernel<TA, KPT, true>,
-                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    ix_launch(linear_recurrence_kernel<TA, KPT, true>, grid, block, smem, stream, (const TA*)q,
-              ldq, (const TA*)k, ldk, (const TA*)v, ldv, decay, bonus, state, cu_q, state_slot,
-              out, H, K, V, KS, q_scale);
-  } else {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(linear_recurrence_kernel<TA, KPT, false>,
-                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    ix_launch(linear_recurrence_kernel<TA, KPT, false>, grid, block, smem, stream, (const TA*)q,
-              ldq, (const TA*)k, ldk, (const TA*)v, ldv, decay, bonus, state, cu_q, state_slot,
-              out, H, K, V, KS, q_scale);
-  }
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (nseg <= 1) {
+      ix_launch(kern, grid, block, smem, stream, (const TA*)q, ldq, (const TA*)k, ldk,
+                (const TA*)v, ldv, decay, bonus, state, cu_q, state_slot, out, H, K, V, KS, q_scale,
+                (int)LR_WHOLE, 0, 1, scr_s, scr_p);
+      return;
+    }
+    ix_launch(kern, grid, block, smem, stream, (const TA*)q, ldq, (const TA*)k, ldk, (const TA*)v,
+              ldv, decay, bonus, state, cu_q, state_slot, out, H, K, V, KS, q_scale,
+              (int)LR_LOCAL, seg_len, nseg, scr_s, scr_p);
+    ix_launch(kern, grid, block, smem, stream, (const TA*)q, ldq, (const TA*)k, ldk, (const TA*)v,
+              ldv, decay, bonus, state, cu_q, state_slot, out, H, K, V, KS, q_scale,
+              (int)LR_JOINED, seg_len, nseg, scr_s, scr_p);
+  };
+  if (bonus_form) go(linear_recurrence_kernel<TA, KPT, true>);
+  else go(linear_recurrence_kernel<TA, KPT, false>);
 }
 
+// seg_len, nseg: 0, 1 for the walk from end to end; otherwise every sequence is cut into
+// segments of seg_len tokens (nseg covers the longest) and `scratch` holds
+// ix_linear_recurrence_scratch_floats(...) floats.
 IX_API int ix_linear_recurrence(const void* q, long long ldq, const void* k, long long ldk,
                                 const void* v, long long ldv, int dtype, const float* decay,
                                 const float* bonus, float* state, const int* cu_q,
                                 const int* state_slot, float* out, int S, int H, int K, int V,
-                                float q_scale, int bonus_form, cudaStream_t stream) {
+                                float q_scale, int bonus_form, int seg_len, int nseg,
+                                float* scratch, cudaStream_t stream) {
   if (S <= 0) return IX_OK;
   if (H <= 0 || K <= 0 || V <= 0 || K > 8 * 64 || H > 65535 || S > 65535) return IX_ERR_SIZE;
   if (bonus_form && !bonus) return IX_ERR_SIZE;
+  if (nseg < 1 || (nseg > 1 && (seg_len <= 0 || !scratch))) return IX_ERR_SIZE;
   const int KS = K > 32 ? 8 : (K > 8 ? 4 : 1);
   const int kpt = (K + KS - 1) / KS;
   const size_t smem =
@@ -263,7 +348,8 @@ IX_API int ix_linear_recurrence(const void* q, long long ldq, const void* k, lon
   IX_DISPATCH_DTYPE(dtype, TA,                                                                  \
                     (launch_recurrence<TA, KPT>(q, ldq, k, ldk, v, ldv, decay, bonus, state,    \
                                                 cu_q, state_slot, out, S, H, K, V, KS, q_scale, \
-                                                bonus_form, smem, stream)))
+                                                bonus_form, smem, seg_len, nseg, scratch,       \
+                                                stream)))
   if (kpt <= 8) LR_GO(8);
   else if (kpt <= 16) LR_GO(16);
   else if (kpt <= 32) LR_GO(32);

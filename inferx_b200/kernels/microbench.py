@@ -348,7 +348,7 @@ def recurrent(args):
     decay = [torch.rand(T, H * K, device="cuda") * 0.1 + 0.9 for _ in range(n)]
     u = torch.randn(H, K, device="cuda")
     low = [torch.randn(T, R, device="cuda") for _ in range(n)]
-    w2 = torch.randn(H * K, R, device="cuda") * 0.1
+    w2 = torch.randn(R, H * K, device="cuda") * 0.1
     b = torch.zeros(H * K, device="cuda")
     o = [torch.randn(T, H, V, device="cuda") for _ in range(n)]
     G = max(1, H // 4)

@@ -1303,14 +1303,22 @@ def add_rmsnorm_sum(resid: torch.Tensor, terms, vector: Optional[torch.Tensor], 
                     eps: float, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None):
     """resid += sum(terms) + vector (kept when ``rows`` is None), then one normed view of the
     rows per gain: RMSNorm(resid) * gain.  ``terms``: up to three tensors shaped like
-    ``resid``, each fp32 or bfloat16 (one that is still unwritten is written out first);
+    ``resid``, each fp32 or bfloat16 (a mixture's output that is still unwritten is combined
+    in the same pass when it has the output's element type, written out first otherwise);
     ``vector``: fp32 [width] added to every row, or None; ``gains``: one or two fp32 [width].
     With ``rows`` the listed rows are gathered and the residual is left as it was."""
     _chk("resid", resid, torch.float32)
     _chk("vector", vector, torch.float32, optional=True)
     _chk("rows", rows, torch.int32, optional=True)
     T, W = resid.shape
-    terms = [t.materialize() if hasattr(t, "materialize") else t for t in terms]
+    # one term may be a mixture's output that was never written; the kernel combines it
+    combine = None
+    for t in terms:
+        if isinstance(t, CombinePending) and combine is None and t.dtype == out_dtype \
+                and t.shape == tuple(resid.shape):
+            combine = t
+    terms = [t.materialize() if hasattr(t, "materialize") else t for t in terms
+             if t is not combine]
     while len(terms) > 3:                      # more than the kernel adds at once
         terms = [terms[0].to(torch.float32) + terms[1].to(torch.float32)] + terms[2:]
     for i, t in enumerate(terms):
@@ -1334,7 +1342,11 @@ def add_rmsnorm_sum(resid: torch.Tensor, terms, vector: Optional[torch.Tensor], 
         _ptr(resid), _ptr(d[0]), codes[0], _ptr(d[1]), codes[1], _ptr(d[2]), codes[2],
         _ptr(vector), _ptr(rows), _ptr(gains[0]), _ptr(gains[1] if len(gains) > 1 else None),
         _ptr(outs[0]), _ptr(outs[1] if len(outs) > 1 else None), _dtype_code(outs[0]), R, W,
-        ctypes.c_float(eps), 1 if rows is None else 0, _stream()), "add_rmsnorm_sum")
+        ctypes.c_float(eps), 1 if rows is None else 0,
+        _ptr(combine.y if combine else None), _ptr(combine.dest if combine else None),
+        _ptr(combine.topk_w if combine else None), _ptr(combine.shared if combine else None),
+        _ptr(combine.shared_logit if combine else None),
+        combine.topk_w.shape[1] if combine else 0, _stream()), "add_rmsnorm_sum")
     _count()
     return tuple(outs)
 
@@ -1405,21 +1417,21 @@ def shift_mix(x: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, step):
 _DECAY_FORMS = {"exp_exp_tanh": 0, "sigmoid_root": 1}
 
 
-def lowrank_decay(x: torch.Tensor, w2: torch.Tensor, b: Optional[torch.Tensor], mode: str,
+def lowrank_decay(x: torch.Tensor, w2t: torch.Tensor, b: Optional[torch.Tensor], mode: str,
                   tau: float = 1.0):
     """fp32 [T, C] decays from the inner activations ``x`` [T, R] of a low-rank product
-    (a view with unit inner stride): z = act(x) . w2^T + b with w2 fp32 [C, R], then
-    "exp_exp_tanh": exp(-exp(z)) with act = tanh; "sigmoid_root": sigmoid(z)^(1/tau) with
-    act the identity."""
-    _chk("w2", w2, torch.float32)
+    (a view with unit inner stride): z = act(x) . w2t + b with the outer matrix transposed,
+    ``w2t`` fp32 [R, C], then "exp_exp_tanh": exp(-exp(z)) with act = tanh; "sigmoid_root":
+    sigmoid(z)^(1/tau) with act the identity."""
+    _chk("w2t", w2t, torch.float32)
     _chk("b", b, torch.float32, optional=True)
     if mode not in _DECAY_FORMS:
         raise KernelError(f"lowrank_decay: unknown form {mode!r}; known: {sorted(_DECAY_FORMS)}")
-    C, R = w2.shape
+    R, C = w2t.shape
     ldx = _row_view("lowrank_decay: x", x, R)
     T = x.shape[0]
     out = torch.empty((T, C), dtype=torch.float32, device=x.device)
-    _check(_lib().ix_lowrank_decay(_ptr(x), _dtype_code(x), ctypes.c_longlong(ldx), _ptr(w2),
+    _check(_lib().ix_lowrank_decay(_ptr(x), _dtype_code(x), ctypes.c_longlong(ldx), _ptr(w2t),
                                    _ptr(b), _ptr(out), T, C, R, _DECAY_FORMS[mode],
                                    ctypes.c_float(tau), _stream()), "lowrank_decay")
     _count()
@@ -1448,13 +1460,42 @@ def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: 
     if bonus_form and (bonus is None or bonus.numel() != heads * dim):
         raise KernelError("linear_recurrence: the bonus form needs u [heads, dim]")
     out = torch.empty((T, heads, vdim), dtype=torch.float32, device=q.device)
+    seg_len, nseg = recurrence_segments(int(getattr(step, "max_q_len", 0) or T), step.num_seqs,
+                                        heads, vdim)
+    scratch = None
+    if nseg > 1:
+        scratch = torch.empty((_lib().ix_linear_recurrence_scratch_floats(
+            step.num_seqs, heads, dim, vdim, nseg),), dtype=torch.float32, device=q.device)
     _check(_lib().ix_linear_recurrence(
         _ptr(q), ctypes.c_longlong(ldq), _ptr(k), ctypes.c_longlong(ldk), _ptr(v),
         ctypes.c_longlong(ldv), _dtype_code(q), _ptr(decay), _ptr(bonus), _ptr(state),
         _ptr(step.cu_q), _ptr(step.state_slot), _ptr(out), step.num_seqs, heads, dim, vdim,
-        ctypes.c_float(q_scale), 1 if bonus_form else 0, _stream()), "linear_recurrence")
-    _count()
+        ctypes.c_float(q_scale), 1 if bonus_form else 0, seg_len, nseg, _ptr(scratch),
+        _stream()), "linear_recurrence")
+    _count(2 if nseg > 1 else 1)
     return out
+
+
+# A sequence's tokens are walked in order by one block per (head, 32 value columns): a long
+# prompt alone leaves most of the GPU idle.  From RECURRENCE_SEGMENT_MIN tokens on, the
+# longest sequence of a step is cut into segments that are walked side by side (one pass
+# for the segments' own states, one that joins them and writes the outputs), as many as
+# fill the multiprocessors about once (RECURRENCE_BLOCKS), none shorter than 64 tokens.
+RECURRENCE_SEGMENT_MIN = 128
+RECURRENCE_BLOCKS = 1024
+RECURRENCE_MAX_SEGMENTS = 64
+
+
+def recurrence_segments(max_q_len: int, num_seqs: int, heads: int, vdim: int):
+    """(tokens per segment, segments) for a step whose longest sequence brings
+    ``max_q_len`` tokens; (0, 1): every sequence is walked from end to end."""
+    if max_q_len < RECURRENCE_SEGMENT_MIN:
+        return 0, 1
+    base = max(1, num_seqs * heads * (-(-vdim // 32)))
+    want = max(1, min(RECURRENCE_MAX_SEGMENTS, RECURRENCE_BLOCKS // base))
+    seg_len = max(64, -(-(-(-max_q_len // want)) // 16) * 16)
+    nseg = -(-max_q_len // seg_len)
+    return (0, 1) if nseg <= 1 else (seg_len, nseg)
 
 
 def check_recurrence_limits(dim: int, where: str = ""):

@@ -13,7 +13,8 @@ the output and the gate's silu are fp32; the projections are the run's matrix pr
 One kernel serves both recurrences (``ops.linear_recurrence``): a sequence's state
 column is owned by one thread from its first token of the step to its last, so a
 position's result does not depend on how the sequence was cut into steps or on what
-else is in the batch.
+else is in the batch; long prompt portions are cut into segments that are walked side by
+side and joined, which changes results by rounding only.
 """
 from __future__ import annotations
 
@@ -64,7 +65,7 @@ class GatedLinearAttention:
         self.front_w = torch.cat([w[f"{p}.q"], w[f"{p}.k"], w[f"{p}.v"], w[f"{p}.g"],
                                   w[f"{p}.a1"]], dim=0).contiguous()
         self.rank = w[f"{p}.a1"].shape[0]
-        self.a2_w, self.a2_b = w[f"{p}.a2"], w[f"{p}.a2.b"]
+        self.a2_t, self.a2_b = w[f"{p}.a2"].t().contiguous(), w[f"{p}.a2.b"]
         self.norm_w, self.o_w = w[f"{p}.norm"], w[f"{p}.o"]
 
     def cache_needs(self):
@@ -77,7 +78,7 @@ class GatedLinearAttention:
         front = ops.linear(x, self.front_w)                  # [T, 2 hk + 2 hv + rank]
         q, k, v = front[:, :hk], front[:, hk:2 * hk], front[:, 2 * hk:2 * hk + hv]
         gate, low = front[:, 2 * hk + hv:2 * hk + 2 * hv], front[:, 2 * hk + 2 * hv:]
-        decay = ops.lowrank_decay(low, self.a2_w, self.a2_b, mode="sigmoid_root",
+        decay = ops.lowrank_decay(low, self.a2_t, self.a2_b, mode="sigmoid_root",
                                   tau=s.tau)                             # fp32 [T, hk]
         o = ops.linear_recurrence(q, k, v, decay, None, cache.state[STATE], step, s.heads,
                                   s.dim, s.vdim, q_scale=s.q_scale,
@@ -120,7 +121,7 @@ class WkvMixer:
         self.rkvg_w = torch.stack([w[f"{p}.{n}"] for n in ("r", "k", "v", "g")]).contiguous()
         self.w1 = w[f"{p}.w1"]
         self.rank = self.w1.shape[0]
-        self.w2, self.w0 = w[f"{p}.w2"], w[f"{p}.w0"]
+        self.w2_t, self.w0 = w[f"{p}.w2"].t().contiguous(), w[f"{p}.w0"]
         self.u = w[f"{p}.u"].contiguous()
         self.norm_w, self.o_w = w[f"{p}.norm"], w[f"{p}.o"]
 
@@ -134,7 +135,7 @@ class WkvMixer:
         mixes = ops.shift_mix(x, self.mu, cache.state[PREVIOUS], step)      # [5, T, hidden]
         rkvg = ops.batched_linear(mixes[:4], self.rkvg_w)                    # [4, T, hk]
         lora = ops.linear(mixes[4], self.w1, out_dtype=torch.float32)                               # [T, rank]
-        decay = ops.lowrank_decay(lora, self.w2, self.w0, mode="exp_exp_tanh")
+        decay = ops.lowrank_decay(lora, self.w2_t, self.w0, mode="exp_exp_tanh")
         o = ops.linear_recurrence(rkvg[0], rkvg[1], rkvg[2], decay, self.u, cache.state[STATE],
                                   step, s.heads, s.dim, s.dim, q_scale=1.0, bonus_form=True)
         y = ops.head_norm_gate(o, self.norm_w, rkvg[3], s.norm_eps, self.ctx.dtype)

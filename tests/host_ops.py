@@ -448,12 +448,12 @@ def shift_mix(x, mu, state, step):
     return out.to(x.dtype)
 
 
-def lowrank_decay(x, w2, b, mode, tau=1.0):
+def lowrank_decay(x, w2t, b, mode, tau=1.0):
     x = _f(x)
     if mode == "exp_exp_tanh":
-        return torch.exp(-torch.exp(torch.tanh(x) @ w2.T + b))
+        return torch.exp(-torch.exp(torch.tanh(x) @ w2t + b))
     assert mode == "sigmoid_root"
-    return torch.exp(torch.nn.functional.logsigmoid(x @ w2.T + b) / tau)
+    return torch.exp(torch.nn.functional.logsigmoid(x @ w2t + b) / tau)
 
 
 def linear_recurrence(q, k, v, decay, bonus, state, step, heads, dim, vdim, q_scale=1.0,

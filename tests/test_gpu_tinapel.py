@@ -109,6 +109,38 @@ def test_summed_norm_pair(dtype, width):
     assert torch.equal(r.cpu(), resid)            # gathered rows leave the stream alone
 
 
+@pytest.mark.parametrize("width", [96, 320, 50])
+def test_summed_norm_takes_an_unwritten_mixture_output(width):
+    """A mixture's output that was never written (expert rows, places, weights, shared
+    part) is combined in the pass that adds and norms; the result is that of writing it
+    out first."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(width)
+    T, k, dt = 9, 3, torch.bfloat16
+    resid = torch.randn(T, width, generator=g)
+    a = torch.randn(T, width, generator=g)
+    y = torch.randn(T * k, width, generator=g).to(dt).cuda()
+    dest = torch.randperm(T * k, generator=g).to(torch.int32).cuda()
+    tw = torch.rand(T, k, generator=g).cuda()
+    shared = torch.randn(T, width, generator=g).to(dt).cuda()
+    g1 = (1.0 + 0.3 * torch.randn(width, generator=g)).cuda()
+    g2 = (1.0 + 0.3 * torch.randn(width, generator=g)).cuda()
+    for sh in (shared, None):
+        pend = ops.CombinePending(y, dest, tw, sh, None)
+        written = ops.moe_combine(y, dest, tw, sh, None)
+        r1, r2 = resid.cuda(), resid.cuda()
+        fused = ops.add_rmsnorm_sum(r1, [a.cuda(), pend], None, (g1, g2), 1e-5, dt)
+        plain_ = ops.add_rmsnorm_sum(r2, [a.cuda(), written], None, (g1, g2), 1e-5, dt)
+        # the written form rounds the combined row to bfloat16 first; the fused one does not
+        torch.testing.assert_close(r1, r2, rtol=1e-2, atol=3e-2)
+        ref = host_ops.add_rmsnorm_sum(resid.clone(), [a, host_ops.moe_combine(
+            y.cpu(), dest.cpu(), tw.cpu(), None if sh is None else sh.cpu(), None).float()], None,
+            (g1.cpu(), g2.cpu()), 1e-5, dt)
+        for o, e, p_ in zip(fused, ref, plain_):
+            torch.testing.assert_close(o.cpu().float(), e.float(), **_tol(dt))
+            torch.testing.assert_close(o.float(), p_.float(), **_tol(dt))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,D,page", [(4, 2, 20, 4), (3, 1, 9, 8), (8, 8, 128, 16), (5, 5, 33, 2)])
 def test_qk_norm_append(dtype, H, G, D, page):
@@ -162,7 +194,7 @@ def test_lowrank_decay(dtype, T, C, R):
     g = torch.Generator().manual_seed(C)
     wide = (torch.randn(T, R + 24, generator=g) * 2.0).to(dtype)
     x = wide[:, 24:]                      # a view into a wider projection
-    w2 = torch.randn(C, R, generator=g)
+    w2 = torch.randn(R, C, generator=g)              # the outer matrix, transposed
     b = torch.randn(C, generator=g) * 2.0
     for mode, tau in (("exp_exp_tanh", 1.0), ("sigmoid_root", 16.0), ("sigmoid_root", 1.0)):
         ref = host_ops.lowrank_decay(x, w2, b, mode, tau)
@@ -195,6 +227,35 @@ def test_linear_recurrence(dtype, H, K, V, bonus):
     assert float((out.cpu() - ref).abs().max()) <= 2e-5 * scale
     assert float((st.cpu() - st_ref).abs().max()) <= 2e-5 * float(st_ref.abs().max())
     assert torch.equal(st.cpu()[3], state[3])     # a slot of no sequence is untouched
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,K,V", [(2, 64, 64), (3, 20, 40), (1, 128, 33)])
+@pytest.mark.parametrize("bonus", [False, True])
+def test_linear_recurrence_in_segments(dtype, H, K, V, bonus):
+    """Long portions are cut into segments that are walked side by side and joined: a long
+    prompt beside a single token, a portion that continues a state, and one whose length is
+    a segment and a token."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(K + V)
+    q_lens = [1, 700, 129, 65]
+    step = _step(q_lens, [40, 0, 300, 0], slots=[3, 0, 2, 1])
+    T = sum(q_lens)
+    assert ops.recurrence_segments(step.max_q_len, len(q_lens), H, V)[1] > 1
+    wide = (torch.randn(T, 2 * H * K + H * V, generator=g) * 0.5).to(dtype)
+    q, k, v = wide[:, :H * K], wide[:, H * K:2 * H * K], wide[:, 2 * H * K:]
+    decay = torch.rand(T, H * K, generator=g) * 0.2 + 0.8
+    u = torch.randn(H, K, generator=g) if bonus else None
+    state = torch.randn(4, H, K, V, generator=g)
+    st_ref = state.clone()
+    ref = host_ops.linear_recurrence(q, k, v, decay, u, st_ref, step, H, K, V, 0.5, bonus)
+    st = state.cuda()
+    wd = wide.cuda()
+    out = ops.linear_recurrence(wd[:, :H * K], wd[:, H * K:2 * H * K], wd[:, 2 * H * K:],
+                                decay.cuda(), None if u is None else u.cuda(), st, _cuda(step),
+                                H, K, V, 0.5, bonus)
+    assert float((out.cpu() - ref).abs().max()) <= 3e-5 * float(ref.abs().max())
+    assert float((st.cpu() - st_ref).abs().max()) <= 3e-5 * float(st_ref.abs().max())
 
 
 def test_linear_recurrence_does_not_depend_on_the_cut():
