@@ -259,6 +259,7 @@ IX_API int ix_add_rmsnorm_sum(float* resid, const void* d0, int c0, const void* 
 // q/k norm + cache write.  One warp per (token, head); heads 0..H-1 are queries, the
 // following G are key/value heads.  qk row layout: [H * D | G * D].
 // ---------------------------------------------------------------------------
+
 #define QKN_WARPS 4
 
 template <typename TA>
@@ -299,6 +300,54 @@ __global__ void qk_norm_append_kernel(const TA* __restrict__ qk, const float* __
   }
 }
 
+// bf16, D a multiple of 8 with D / 8 a power of two up to 32: GL = D / 8 lanes share a
+// head, each with eight values in one 16-byte access, 32 / GL heads a warp.
+template <int GL>
+__global__ void qk_norm_append_bf16_vec_kernel(
+    const bf16* __restrict__ qk, const float* __restrict__ q_gain,
+    const float* __restrict__ k_gain, const int* __restrict__ positions, bf16* __restrict__ q_out,
+    bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, const int* __restrict__ slots, int H,
+    int G, int D, int page_size, float eps, float temp_coef, int temp_every) {
+  IX_PDL_WAIT();
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31;
+  constexpr int HPW = 32 / GL;
+  const int j = (blockIdx.y * QKN_WARPS + (threadIdx.x >> 5)) * HPW + lane / GL;
+  const int sub = lane % GL;
+  const bool ok = j < H + G;
+  float f[8];
+  uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+  if (ok) raw = reinterpret_cast<const uint4*>(qk + (size_t)t * (H + G) * D + (size_t)j * D)[sub];
+  bf8_to_f32(raw, f);
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+#pragma unroll
+  for (int d = GL / 2; d > 0; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+  if (!ok) return;
+  const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+  float g[8];
+  if (j < H) {
+    float temp = 1.0f;
+    if (temp_every > 0)
+      temp = 1.0f + temp_coef * logf((float)((positions[t] + 1) / temp_every) + 1.0f);
+    load8_any(q_gain, IX_F32, sub, g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = f[i] * inv * g[i] * temp;
+    reinterpret_cast<uint4*>(q_out + ((size_t)t * H + j) * D)[sub] = f32_to_bf8(f);
+  } else if (k_cache) {
+    const int slot = slots[t];
+    if (slot < 0) return;
+    const size_t base =
+        (((size_t)(slot / page_size) * G + (j - H)) * page_size + slot % page_size) * D;
+    reinterpret_cast<uint4*>(v_cache + base)[sub] = raw;
+    load8_any(k_gain, IX_F32, sub, g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = f[i] * inv * g[i];
+    reinterpret_cast<uint4*>(k_cache + base)[sub] = f32_to_bf8(f);
+  }
+}
+
 IX_API int ix_qk_norm_append(const void* qk, int dtype, const float* q_gain, const float* k_gain,
                              const int* positions, void* q_out, void* k_cache, void* v_cache,
                              const int* slots, int T, int H, int G, int D, int page_size,
@@ -308,6 +357,25 @@ IX_API int ix_qk_norm_append(const void* qk, int dtype, const float* q_gain, con
   if ((k_cache != nullptr) != (v_cache != nullptr) || (k_cache && !slots)) return IX_ERR_SIZE;
   const int groups = (H + G + QKN_WARPS - 1) / QKN_WARPS;
   if (groups > 65535) return IX_ERR_SIZE;
+  const int gl = D / 8;
+  if (dtype == IX_BF16 && D % 8 == 0 && gl <= 32 && (gl & (gl - 1)) == 0 &&
+      (((uintptr_t)qk | (uintptr_t)q_gain | (uintptr_t)k_gain | (uintptr_t)q_out |
+        (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0) {
+    const int hpb = QKN_WARPS * (32 / gl);
+    const int vgroups = (H + G + hpb - 1) / hpb;
+#define IX_QKN(GL)                                                                              \
+  ix_launch(qk_norm_append_bf16_vec_kernel<GL>, dim3(T, vgroups), dim3(32 * QKN_WARPS), 0,      \
+            stream, (const bf16*)qk, q_gain, k_gain, positions, (bf16*)q_out, (bf16*)k_cache,   \
+            (bf16*)v_cache, slots, H, G, D, page_size, eps, temp_coef, temp_every)
+    if (gl == 32) IX_QKN(32);
+    else if (gl == 16) IX_QKN(16);
+    else if (gl == 8) IX_QKN(8);
+    else if (gl == 4) IX_QKN(4);
+    else if (gl == 2) IX_QKN(2);
+    else IX_QKN(1);
+#undef IX_QKN
+    return ix_launch_status();
+  }
   IX_DISPATCH_DTYPE(dtype, TA,
                     ix_launch(qk_norm_append_kernel<TA>, dim3(T, groups), dim3(32 * QKN_WARPS), 0,
                               stream, (const TA*)qk, q_gain, k_gain, positions, (TA*)q_out,
