@@ -330,6 +330,7 @@ linear_recurrence_kernel(const TA* __restrict__ q, long long ldq, const TA* __re
     if (prefetch && t0 + LR_CHUNK < t_end)
       fetch(t0 + LR_CHUNK, min(LR_CHUNK, t_end - t0 - LR_CHUNK));
     if (mode == LR_LOCAL) {
+#pragma unroll 4
       for (int c = 0; c < n; ++c) {
         const float vj = v_s[c * LR_COLS + lane];
         const float* kc = k_s + c * K + kk0;
@@ -360,6 +361,7 @@ linear_recurrence_kernel(const TA* __restrict__ q, long long ldq, const TA* __re
       __syncthreads();
       continue;
     }
+#pragma unroll 4
     for (int c = 0; c < n; ++c) {
       const float vj = v_s[c * LR_COLS + lane];
       const float* qc = q_s + c * K + kk0;
