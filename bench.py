@@ -825,15 +825,15 @@ def tinapel_configs(z, layers, pattern):
            "shared": {"ff": z["shared"]}}
     kinds = {
         "wkv": {"type": "wkv", "mixer": {"heads": W // 64, "dim": 64, "rank": 64}, "mlp": mlp},
-        "gla": {"type": "gla", "mixer": {"heads": W // 128, "dim": 64, "vdim": 128, "tau": 16.0,
-                                         "rank": 16}, "mlp": mlp},
+        "gla": {"type": "gla", "mixer": {"heads": W // 128, "dim": 64, "vdim": 128, "tau": 8.0,
+                                         "rank": 32}, "mlp": mlp},
         "attention": {"type": "attention",
                       "mixer": {"heads": z["heads"], "kv_heads": z["kv"], "dim": 128, "vdim": 128,
-                                "scale": 1.0 / math.sqrt(128.0), "softcap": 50.0,
+                                "scale": 1.0 / math.sqrt(128.0), "softcap": 30.0,
                                 "q_temp": {"coef": 0.1, "every": 1024}}, "mlp": mlp},
     }
     new = {"architecture": "Tinapel", "vocab": DESIGN_VOCAB, "width": W,
-           "embedding": {"scale": math.sqrt(W)}, "norm": {"eps": 1e-6},
+           "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
            "layers": [kinds[pattern[i % len(pattern)]] for i in range(layers)]}
     twin = {"architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",
             "num_hidden_layers": layers, "hidden_size": W,

@@ -13,7 +13,7 @@
     python -m inferx_b200.kernels.microbench rowwise --tokens 4096 --hidden 2048 --inter 5632
     python -m inferx_b200.kernels.microbench recurrent --tokens 4096 --batch 1 --hidden 2048 --head-dim 64
     python -m inferx_b200.kernels.microbench recurrent --tokens 64 --batch 64 --hidden 2048 --head-dim 64
-    python -m inferx_b200.kernels.microbench attn_prefill --tokens 2048 --softcap 50
+    python -m inferx_b200.kernels.microbench attn_prefill --tokens 2048 --softcap 30
 
 Each case runs one kernel face at Qwen1.5-MoE-A2.7B sizes (or the sizes given),
 cycling through enough copies of its inputs that consecutive iterations do not

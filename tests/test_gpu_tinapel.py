@@ -109,14 +109,14 @@ def test_summed_norm_pair(dtype, width):
     assert torch.equal(r.cpu(), resid)            # gathered rows leave the stream alone
 
 
-@pytest.mark.parametrize("width", [96, 320, 50])
+@pytest.mark.parametrize("width", [96, 328, 50])
 def test_summed_norm_takes_an_unwritten_mixture_output(width):
     """A mixture's output that was never written (expert rows, places, weights, shared
     part) is combined in the pass that adds and norms; the result is that of writing it
     out first."""
     ops = _ops()
     g = torch.Generator().manual_seed(width)
-    T, k, dt = 9, 3, torch.bfloat16
+    T, k, dt = 9, 2, torch.bfloat16
     resid = torch.randn(T, width, generator=g)
     a = torch.randn(T, width, generator=g)
     y = torch.randn(T * k, width, generator=g).to(dt).cuda()
@@ -189,14 +189,14 @@ def test_shift_mix(dtype, width):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T,C,R", [(9, 128, 16), (1, 35, 3), (70, 512, 64), (17, 300, 1)])
+@pytest.mark.parametrize("T,C,R", [(9, 136, 12), (1, 35, 3), (70, 512, 64), (17, 300, 1)])
 def test_lowrank_decay(dtype, T, C, R):
     g = torch.Generator().manual_seed(C)
     wide = (torch.randn(T, R + 24, generator=g) * 2.0).to(dtype)
     x = wide[:, 24:]                      # a view into a wider projection
     w2 = torch.randn(R, C, generator=g)              # the outer matrix, transposed
     b = torch.randn(C, generator=g) * 2.0
-    for mode, tau in (("exp_exp_tanh", 1.0), ("sigmoid_root", 16.0), ("sigmoid_root", 1.0)):
+    for mode, tau in (("exp_exp_tanh", 1.0), ("sigmoid_root", 12.0), ("sigmoid_root", 1.0)):
         ref = host_ops.lowrank_decay(x, w2, b, mode, tau)
         out = _ops().lowrank_decay(wide.cuda()[:, 24:], w2.cuda(), b.cuda(), mode, tau)
         torch.testing.assert_close(out.cpu(), ref, rtol=2e-5, atol=2e-6)

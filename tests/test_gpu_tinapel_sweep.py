@@ -32,13 +32,13 @@ def draw_layer(rng):
                       rng.choice([1, 4, 16, 40]), draw_mlp(rng))
     if kind == "gla":
         return tc.gla(rng.choice([1, 2, 4, 6]), rng.choice([4, 8, 20, 32, 64, 100]),
-                      rng.choice([4, 12, 32, 64, 128, 37]), rng.choice([1.0, 4.0, 16.0]),
+                      rng.choice([4, 12, 32, 64, 128, 37]), rng.choice([1.0, 4.0, 12.0]),
                       rng.choice([2, 8, 16, 33]), draw_mlp(rng))
     kv = rng.choice([1, 1, 2, 3])
     dim = rng.choice([9, 16, 20, 32, 64, 64, 96, 128, 128])
     return tc.attention(kv * rng.choice([1, 2, 4]), kv, dim, rng.choice([0.1, 0.3, dim ** -0.5]),
-                        softcap=rng.choice([0.0, 3.0, 30.0, 50.0]),
-                        q_temp=rng.choice([None, (0.3, 5), (0.1, 64), (0.7, 1)]),
+                        softcap=rng.choice([0.0, 3.0, 30.0, 40.0]),
+                        q_temp=rng.choice([None, (0.35, 5), (0.1, 64), (0.7, 1)]),
                         mlp=draw_mlp(rng))
 
 

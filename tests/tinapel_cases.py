@@ -78,8 +78,8 @@ TD = {
     "norm": {"eps": 1e-5},
     "layers": [
         wkv(4, 64, 32, moe(8, 2, 128, 1.0, shared=128)),
-        gla(2, 64, 128, 16.0, 16, moe(8, 2, 128, 1.0, shared=128)),
-        attention(8, 2, 64, 0.125, softcap=20.0, q_temp=(0.3, 32), mlp=moe(8, 2, 128, 2.0, shared=256)),
+        gla(2, 64, 128, 12.0, 24, moe(8, 2, 128, 1.0, shared=128)),
+        attention(8, 2, 64, 0.125, softcap=20.0, q_temp=(0.25, 32), mlp=moe(8, 2, 128, 2.0, shared=256)),
         attention(4, 1, 128, 0.09, q_temp=(0.1, 10), mlp=moe(4, 4, 64, 1.0)),
     ],
     "loop": {"start": 0, "stop": 4, "times": 2},
