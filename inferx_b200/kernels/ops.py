@@ -1114,6 +1114,12 @@ def gate_up_glu_clamped(x: torch.Tensor, w_gate_up: torch.Tensor, limit: float, 
     return glu_clamped(linear(x, w_gate_up), limit, alpha, up_shift)
 
 
+# From this many weights a matrix, a batched product of at most 16 rows a matrix streams the
+# weights with this library's kernel (per-head products of a few ten thousand weights stay
+# with the library, where they measured equal or faster).
+BATCHED_STREAM_MIN_WEIGHTS = 1 << 20
+
+
 def batched_linear(x: torch.Tensor, w: torch.Tensor):
     """out[b] = x[b] . w[b]^T for x [B, M, K] (any strides with unit inner stride) and
     w [B, N, K]: one library call batched over the leading dimension (per-head
@@ -1129,6 +1135,16 @@ def batched_linear(x: torch.Tensor, w: torch.Tensor):
                           f"{tuple(w.shape)} {w.dtype}")
     if x.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
         raise KernelError("batched_linear: TF32 is switched on; 32-bit products must be exact")
+    B, M, K = x.shape
+    if (M <= SMALL_M_DENSE_ROWS and w.shape[1] * K >= BATCHED_STREAM_MIN_WEIGHTS
+            and x.is_contiguous() and w.is_contiguous() and _streams_weights(x, w)):
+        # a few rows against large matrices: each matrix is a group of the weight-streaming
+        # kernel, its rows one pass (the library's batched product reads such weights at a
+        # fraction of the memory rate)
+        offsets = torch.arange(0, (B + 1) * M, M, dtype=torch.int32, device=x.device)
+        out = gemm_small_m(x.view(B * M, K), w, None, offsets, False, B * M,
+                           rows_per_pass=8 if M <= 8 else 16, active_groups=B)
+        return out.view(B, M, w.shape[1])
     LIBRARY_CALLS[0] += 1
     return torch.bmm(x, w.transpose(1, 2))
 

@@ -301,6 +301,19 @@ def test_head_norm_gate(dtype, H, V, per_head):
     torch.testing.assert_close(out.cpu().float(), ref.float(), **_tol(dtype))
 
 
+@pytest.mark.parametrize("M", [1, 8, 13, 16, 17])
+def test_batched_product_of_a_few_rows_against_large_matrices(M):
+    """Up to 16 rows a matrix stream the weights; more go to the library; both are the
+    batched product."""
+    g = torch.Generator().manual_seed(M)
+    x = (torch.randn(4, M, 1024, generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(4, 1032, 1024, generator=g) * 0.05).to(torch.bfloat16)
+    ref = torch.bmm(x.float(), w.float().transpose(1, 2))
+    out = _ops().batched_linear(x.cuda(), w.cuda())
+    assert out.shape == (4, M, 1032) and out.dtype == torch.bfloat16
+    torch.testing.assert_close(out.cpu().float(), ref, rtol=1.6e-2, atol=1.6e-2)
+
+
 def _kv_case(seed, H, G, D, page, q_lens, starts, dtype):
     g = torch.Generator().manual_seed(seed)
     step = _step(q_lens, starts)
