@@ -39,3 +39,20 @@ def test_decode_attention_splits_are_bounded_and_follow_the_context(lib):
                 last = n
         # one sequence needs many runs to fill the device, 64 sequences hardly any
         assert pick(1, 16, 16, 32768) >= 8 > pick(64, 16, 16, 32768)
+
+
+def test_recurrence_is_cut_into_segments_only_for_long_portions():
+    f = ops.recurrence_segments                # (longest portion, sequences, heads, value size)
+    assert f(1, 64, 32, 64) == (0, 1) and f(127, 1, 4, 64) == (0, 1)      # walked end to end
+    assert f(2048, 1, 32, 64) == (128, 16)     # 64 (head, value tile) items x 16 segments
+    assert f(4096, 1, 32, 64) == (256, 16)
+    assert f(300, 64, 32, 64) == (0, 1)        # many sequences fill the device themselves
+    for tokens in (128, 129, 500, 1119, 5000, 100000):
+        for seqs in (1, 3, 16):
+            for heads in (1, 4, 32):
+                seg_len, nseg = f(tokens, seqs, heads, 64)
+                if nseg == 1:
+                    assert seg_len == 0
+                    continue
+                assert seg_len >= 64 and seg_len % 16 == 0 and 2 <= nseg <= 64
+                assert (nseg - 1) * seg_len < tokens <= nseg * seg_len    # the segments cover it
