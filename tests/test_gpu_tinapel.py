@@ -399,6 +399,24 @@ def test_long_decoding_with_recorded_steps(tmp_path, dtype):
     mc.compare(rows, ref, tc.bound_for(dtype, d, reqs), f"long decode {dtype}")
 
 
+@pytest.mark.parametrize("dtype,kind", [("bfloat16", "whole"), ("bfloat16", "mixed"),
+                                        ("float32", "tail")])
+def test_long_prompts_at_tensor_core_sizes(tmp_path, dtype, kind):
+    """Prompts of several hundred tokens at head sizes 64 and 128: the recurrence walks them
+    in segments, attention runs on the tcgen05 and TMA kernels with squashed scores and cuts
+    long contexts into runs, the temperature passes many of its steps."""
+    cfg = tc.TD
+    d = tc.make_model_dir(cfg, tmp_path / "m", 11,
+                          dtype="float32" if dtype == "float32" else "bfloat16")
+    reqs = tc.make_requests(cfg, [600, 260], 11)
+    ref = tc.reference_rows(d, reqs)
+    steps = mc.TRACE_KINDS[kind](reqs)
+    sess = ReplaySession(d, dtype, traces.peak_tokens(steps), page_size=16, max_live=4)
+    rows = mc.run_trace(sess, steps)
+    sess.executor.poll_errors()
+    mc.compare(rows, ref, tc.bound_for(dtype, d, reqs), f"long/{kind}/{dtype}")
+
+
 def test_prefill_equals_decoding_in_32_bit(tmp_path):
     """The same sequence whole, token by token and in portions of two: the three runs
     agree with each other far inside their distance to the plain model."""
