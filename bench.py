@@ -932,8 +932,8 @@ def main(argv=None):
     ap.add_argument("--prefill-tokens", type=int, default=0,
                     help="with --marginal: a prompt step of this many tokens instead")
     ap.add_argument("--designs", action="store_true",
-                    help="prompt and decode throughput of the Zuzisun design beside Qwen2-MoE "
-                         "with dense layers at equal sizes (random weights); --layers (4), "
+                    help="prompt and decode throughput of a design (--design, Zuzisun by default) "
+                         "beside the closest Qwen2-MoE at equal sizes (random weights); --layers (4), "
                          "--batch, --context (4096), --prefill-tokens (2048) apply")
     ap.add_argument("--design-sizes", default="", help="with --designs: of 1k,2k,4k (all)")
     ap.add_argument("--design", default="zuzisun", choices=["zuzisun", "tinapel"],
