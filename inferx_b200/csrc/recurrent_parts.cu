@@ -212,6 +212,25 @@ IX_API int ix_lowrank_decay(const void* x, int x_dtype, long long ldx, const flo
 #define LR_PF 4
 enum { LR_WHOLE = 0, LR_LOCAL = 1, LR_JOINED = 2 };
 
+// One state entry, one token.  The roundings are spelled out (one product, two fused
+// multiply-adds; three in the bonus form), so that every path through the kernel - staged
+// chunks, vector reads, the single-token form, the pass without outputs - rounds alike.
+template <bool BONUS>
+__device__ __forceinline__ void lr_step(float& S, float u, float kk, float w, float q, float vj,
+                                        float& acc) {
+  const float kv = __fmul_rn(kk, vj);
+  if (BONUS) {
+    acc = __fmaf_rn(__fmaf_rn(u, kv, S), q, acc);
+    S = __fmaf_rn(w, S, kv);
+  } else {
+    S = __fmaf_rn(w, S, kv);
+    acc = __fmaf_rn(S, q, acc);
+  }
+}
+__device__ __forceinline__ void lr_step_local(float& S, float kk, float w, float vj) {
+  S = __fmaf_rn(w, S, __fmul_rn(kk, vj));
+}
+
 template <typename TA, int KPT, bool BONUS, int MODE>
 __global__ void __launch_bounds__(LR_COLS * 8, KPT <= 8 ? 4 : (KPT <= 16 ? 3 : 1))
 linear_recurrence_kernel(const TA* __restrict__ q, long long ldq, const TA* __restrict__ k,
@@ -275,6 +294,38 @@ linear_recurrence_kernel(const TA* __restrict__ q, long long ldq, const TA* __re
   }
   if (!walks) return;
 
+  // A sequence that brings one token (a decode step): nothing is staged.  Every thread reads
+  // its slice of q, k and the decay straight from global memory (the lanes of a warp read
+  // the same addresses), the slices' partial outputs meet in shared memory once.  The same
+  // operations in the same order as the walk below, so the same bits.
+  if (mode == LR_WHOLE && t_end - t_begin == 1) {
+    const size_t t = (size_t)t_begin;
+    const float vj = col_ok ? to_f32(v[t * ldv + (size_t)h * V + col]) : 0.f;
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < KPT; ++i) {
+      const int kk = kk0 + i;
+      if (kk < K) {
+        const float qv = __fmul_rn(to_f32(q[t * ldq + (size_t)h * K + kk]), q_scale);
+        lr_step<BONUS>(S[i], u[i], to_f32(k[t * ldk + (size_t)h * K + kk]),
+                       decay[(t * H + h) * K + kk], qv, vj, acc);
+      }
+    }
+    part[ks * LR_COLS + lane] = acc;
+    __syncthreads();
+    if (ks == 0 && col_ok) {
+      float total = 0.f;
+      for (int w = 0; w < KS; ++w) total += part[w * LR_COLS + lane];
+      out[(t * H + h) * V + col] = total;
+    }
+#pragma unroll
+    for (int i = 0; i < KPT; ++i) {
+      const int kk = kk0 + i;
+      if (kk < K && col_ok) st[(size_t)kk * V + col] = S[i];
+    }
+    return;
+  }
+
   // Where a chunk's inputs are at most LR_PF values a thread (key sizes up to 64 with eight
   // warps), the next chunk is fetched into registers while this one is walked, so that the
   // latency of global memory is not waited for at every chunk.
@@ -288,7 +339,7 @@ linear_recurrence_kernel(const TA* __restrict__ q, long long ldq, const TA* __re
       if (i < n * K) {
         const int c = i / K, kk = i % K;
         const size_t t = (size_t)(t0 + c);
-        if (mode != LR_LOCAL) pq[e] = to_f32(q[t * ldq + (size_t)h * K + kk]) * q_scale;
+        if (mode != LR_LOCAL) pq[e] = __fmul_rn(to_f32(q[t * ldq + (size_t)h * K + kk]), q_scale);
         pk[e] = to_f32(k[t * ldk + (size_t)h * K + kk]);
         pw[e] = decay[(t * H + h) * K + kk];
       }
@@ -317,7 +368,7 @@ linear_recurrence_kernel(const TA* __restrict__ q, long long ldq, const TA* __re
       for (int i = threadIdx.x; i < n * K; i += blockDim.x) {
         const int c = i / K, kk = i % K;
         const size_t t = (size_t)(t0 + c);
-        if (mode != LR_LOCAL) q_s[i] = to_f32(q[t * ldq + (size_t)h * K + kk]) * q_scale;
+        if (mode != LR_LOCAL) q_s[i] = __fmul_rn(to_f32(q[t * ldq + (size_t)h * K + kk]), q_scale);
         k_s[i] = to_f32(k[t * ldk + (size_t)h * K + kk]);
         w_s[i] = decay[(t * H + h) * K + kk];
       }
@@ -341,10 +392,10 @@ linear_recurrence_kernel(const TA* __restrict__ q, long long ldq, const TA* __re
             if (kk0 + i < K) {
               const float4 k4 = *reinterpret_cast<const float4*>(kc + i);
               const float4 w4 = *reinterpret_cast<const float4*>(wc + i);
-              S[i] = w4.x * S[i] + k4.x * vj;
-              S[i + 1] = w4.y * S[i + 1] + k4.y * vj;
-              S[i + 2] = w4.z * S[i + 2] + k4.z * vj;
-              S[i + 3] = w4.w * S[i + 3] + k4.w * vj;
+              lr_step_local(S[i], k4.x, w4.x, vj);
+              lr_step_local(S[i + 1], k4.y, w4.y, vj);
+              lr_step_local(S[i + 2], k4.z, w4.z, vj);
+              lr_step_local(S[i + 3], k4.w, w4.w, vj);
               P[i] *= w4.x; P[i + 1] *= w4.y; P[i + 2] *= w4.z; P[i + 3] *= w4.w;
             }
           }
@@ -352,7 +403,7 @@ linear_recurrence_kernel(const TA* __restrict__ q, long long ldq, const TA* __re
 #pragma unroll
           for (int i = 0; i < KPT; ++i) {
             if (kk0 + i < K) {
-              S[i] = wc[i] * S[i] + kc[i] * vj;
+              lr_step_local(S[i], kc[i], wc[i], vj);
               P[i] *= wc[i];
             }
           }
@@ -368,17 +419,7 @@ linear_recurrence_kernel(const TA* __restrict__ q, long long ldq, const TA* __re
       const float* kc = k_s + c * K + kk0;
       const float* wc = w_s + c * K + kk0;
       float acc = 0.f;
-#define LR_STEP(SI, UI, KV, WV, QV)          \
-  {                                          \
-    const float kv = (KV) * vj;              \
-    if (BONUS) {                             \
-      acc += ((SI) + (UI) * kv) * (QV);      \
-      (SI) = (WV) * (SI) + kv;               \
-    } else {                                 \
-      (SI) = (WV) * (SI) + kv;               \
-      acc += (SI) * (QV);                    \
-    }                                        \
-  }
+#define LR_STEP(SI, UI, KV, WV, QV) lr_step<BONUS>(SI, UI, KV, WV, QV, vj, acc);
       if (vec4) {        // K a multiple of 4: four channels a shared-memory read
 #pragma unroll
         for (int i = 0; i < KPT; i += 4) {
